@@ -1,0 +1,347 @@
+#!/usr/bin/env python
+"""Benchmark of the fused GRPO token loss (fwd+bwd) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1] [--impl ours|reference]
+
+One step = one forward+backward pass of the loss over one batch of synthetic logits that is
+already resident in HBM.  N=1 runs the Qwen2.5-7B-shaped workload (32768 x 151936 bf16).
+N>1 (launched by torch.distributed.run, one rank per GPU) runs the same global shape
+vocabulary-sharded: V/N columns per rank, one NCCL all-gather of the per-token partials.
+Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of the
+reference's jnp expressions (the reference itself needs JAX, which is not installable here).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "fused GRPO loss fwd+bwd tokens/s"
+UNIT = "tokens/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="cfg1")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-sample-tokens", type=int, default=512)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--seed", type=int, default=0)
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def oracle_inputs(data):
+    """Aligned synthetic batch -> the reference's shifted inputs dict (one dummy leading position)."""
+    ids, mask = data["token_ids"], data["mask"]
+    B = ids.shape[0]
+    z = torch.zeros(B, 1, dtype=ids.dtype)
+    return {"input_ids": torch.cat([z, ids.cpu()], 1), "labels": torch.cat([z, mask.cpu().to(ids.dtype)], 1),
+            "advantages": data["advantages"].cpu(), "total_valid_token_count": data["total_valid"],
+            "old_per_token_logps": data["old_logps"].cpu(), "ref_per_token_logps": data["ref_logps"].cpu()}
+
+
+def cpu_baseline(args, w, steps=None, warmup=1):
+    """Times the CPU restatement on a bounded sample of the same workload (rank 0 only).
+    steps=None: repeat for about 10 s (at least 3 passes); else exactly `steps` passes."""
+    from mllm_jax_b200 import synth
+    from oracle import grpo_oracle as O
+
+    nseq = max(1, args.cpu_sample_tokens // 64)
+    sample = synth.scaled(w, n_seqs=nseq, seq_len=64, len_lo=16, len_hi=64, group=min(w.group, nseq))
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    data = synth.make_inputs(sample, seed=1)
+    inputs = oracle_inputs(data)
+    logits = torch.cat([data["logits"], data["logits"][:, :1]], 1)  # the unscored last position
+    attrs = dict(beta=w.beta, epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high, softcap=w.softcap)
+    # shift: row i scores token i+1, so oracle_inputs prepends a dummy id/label and a dummy last row is appended
+    for _ in range(max(1, warmup)):
+        O.reference_value_and_grad(logits, inputs, **attrs)
+    t0 = time.perf_counter()
+    reps = 0
+    while (reps < steps) if steps else (reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 50)):
+        O.reference_value_and_grad(logits, inputs, **attrs)
+        reps += 1
+    sec = (time.perf_counter() - t0) / reps
+    return {"value": sample.n_tokens / sec, "unit": UNIT, "cores": cores, "kind": "port", "ms_per_pass": sec * 1e3,
+            "sample": f"{sample.n_tokens} tokens x V={w.vocab} per pass, {reps} passes, torch-CPU restatement + autograd"}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import mllm_jax_b200 as G
+    from mllm_jax_b200 import _lib, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the GRPO loss kernels have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    w = synth.CONFIGS[args.workload]
+    cfg = G.LossConfig(epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high, beta=w.beta, softcap=w.softcap)
+    N, V = w.n_tokens, w.vocab
+
+    if world == 1:
+        data = synth.make_inputs(w, seed=args.seed, device=str(dev))
+        dlogits = torch.empty_like(data["logits"])
+
+        def step():
+            return G.grpo_value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
+                                         data["total_valid"], data["old_logps"], data["ref_logps"], cfg=cfg,
+                                         dlogits=dlogits)
+        parallelism = "single"
+    else:
+        from mllm_jax_b200.vocab_parallel import VocabParallelLoss
+
+        data = synth.make_inputs(w, seed=args.seed, device=str(dev), vocab_shard=(rank, world))
+        vp = VocabParallelLoss(V, cfg)
+        # exact log-probs of the sharded rows come from one forward of the same exchange
+        p0 = vp.problem(data["logits"], data["token_ids"], data["mask"], data["advantages"], data["total_valid"])
+        vp.forward(p0)
+        lp = p0.per_token_logps.clone()
+        data["old_logps"] = lp + (data["old_logps"] - data["exact_logps"])
+        data["ref_logps"] = lp + (data["ref_logps"] - data["exact_logps"])
+        dlogits = torch.empty_like(data["logits"])
+
+        def step():
+            return vp.value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
+                                     data["total_valid"], data["old_logps"], data["ref_logps"], dlogits=dlogits)
+        parallelism = f"vocab-parallel tp{world}"
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    launches0 = _lib.launch_count()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        out = step()
+    ev1.record()
+    barrier()
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms = ev0.elapsed_time(ev1)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = N / (ms_per_step * 1e-3)
+    loss = float(out["loss"].item())
+
+    # Per-kernel timing of the two streaming passes (same buffers), for the roofline of the dominant one.
+    prob = out["problem"]
+    fwd_entry = "mllm_grpo_fwd" if world == 1 else "mllm_grpo_fwd_partials"
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    t_f, t_b = [], []
+    for i in range(3 + args.steps):
+        evs[0].record()
+        prob.run(fwd_entry)
+        evs[1].record()
+        prob.run("mllm_grpo_bwd")
+        evs[2].record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            t_f.append(evs[0].elapsed_time(evs[1]))
+            t_b.append(evs[1].elapsed_time(evs[2]))
+    ms_f, ms_b = sum(t_f) / len(t_f), sum(t_b) / len(t_b)
+    peak, peak_kind = peaks()
+    v_local = V // world
+    bytes_bwd = 4.0 * v_local * N  # read logits + write dlogits, bf16 (zero rows counted in full)
+    bytes_fwd = 2.0 * v_local * N
+    ach_b = bytes_bwd / (ms_b * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "dlogits_kernel (backward sweep)", "achieved": ach_b, "peak": peak,
+                "unit": "GB/s", "frac": ach_b / peak, "peak_kind": peak_kind, "traffic": None,
+                "ms_per_launch": ms_b, "algorithmic_bytes_per_launch": bytes_bwd,
+                "fwd_kernel": {"ms_per_launch": ms_f, "achieved": bytes_fwd / (ms_f * 1e-3) / 1e9,
+                               "frac": bytes_fwd / (ms_f * 1e-3) / 1e9 / peak},
+                "step": {"algorithmic_bytes": 6.0 * v_local * N,
+                         "achieved": 6.0 * v_local * N / (ms_per_step * 1e-3) / 1e9,
+                         "frac": 6.0 * v_local * N / (ms_per_step * 1e-3) / 1e9 / peak,
+                         "frac_of_8TBs": 6.0 * v_local * N / (ms_per_step * 1e-3) / 1e9 / 8000.0}}
+
+    e2e = None
+    if not args.no_e2e and world == 1:
+        e2e = measure_e2e(G, data, cfg, dlogits, args, dev)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        del data, dlogits
+        torch.cuda.empty_cache()
+        cpu = cpu_baseline(args, w)
+
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 in / f32 accumulate", "data": "synthetic",
+            "config": {"workload": w.name, "rows": N, "vocab": V, "global_batch": w.n_seqs, "seq_len": w.seq_len,
+                       "parallelism": parallelism, "l2": "inputs (%.1f GB per GPU) exceed the 126 MB L2" %
+                       (2.0 * v_local * N / 1e9), "mask_valid_fraction": prob.mask.mean().item(),
+                       "epsilon": [w.epsilon_low, w.epsilon_high], "beta": w.beta, "softcap": w.softcap},
+            "loss": loss, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks,
+        }))
+
+
+def measure_e2e(G, data, cfg, dlogits, args, dev):
+    """Same metric through the public API with HOST buffers: per step, copy the step's inputs from
+    pinned host memory, run fwd+bwd, read loss and per-token log-probs back."""
+    names = ("logits", "token_ids", "mask", "advantages", "old_logps", "ref_logps")
+    host = {}
+    try:
+        for k in names:
+            host[k] = torch.empty(data[k].shape, dtype=data[k].dtype, pin_memory=True)
+            host[k].copy_(data[k])
+    except RuntimeError as e:  # not enough pinnable host memory
+        return {"value": None, "unit": UNIT, "error": str(e)[:120]}
+    torch.cuda.synchronize()
+    N = data["token_ids"].numel()
+    lp_host = torch.empty(data["token_ids"].shape, dtype=torch.float32, pin_memory=True)
+    loss_host = torch.empty((), dtype=torch.float32, pin_memory=True)
+    steps = max(2, min(args.steps, 5))
+    h2d = sum(host[k].numel() * host[k].element_size() for k in names)
+    d2h = lp_host.numel() * 4 + 4
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(1 + steps):
+        if i == 1:
+            torch.cuda.synchronize()
+            ev0.record()
+        for k in names:
+            data[k].copy_(host[k], non_blocking=True)
+        out = G.grpo_value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
+                                    data["total_valid"], data["old_logps"], data["ref_logps"], cfg=cfg,
+                                    dlogits=dlogits)
+        lp_host.copy_(out["per_token_logps"], non_blocking=True)
+        loss_host.copy_(out["loss"], non_blocking=True)
+        torch.cuda.synchronize()
+    ev1.record()
+    torch.cuda.synchronize()
+    sec = ev0.elapsed_time(ev1) * 1e-3 / steps
+    return {"value": N / sec, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "ms_per_step": sec * 1e3, "steps": steps,
+            "note": "logits cross PCIe every step; dlogits stay on the device for the lm_head backward"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from mllm_jax_b200 import synth
+
+    w = synth.CONFIGS[args.workload]
+    t_all = time.perf_counter()
+    cb = cpu_baseline(args, w, steps=args.steps, warmup=min(args.warmup, 2))
+    value = cb["value"]
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_pass"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "sample": cb["sample"]},
+        "cpu_baseline": cb,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t_all,
+    }))
+
+
+if __name__ == "__main__":
+    main()

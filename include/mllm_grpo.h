@@ -1,0 +1,170 @@
+/*
+ * mllm_grpo.h -- C ABI of the B200 (sm_100a) fused GRPO / PPO-clip token loss.
+ *
+ * The library replaces one region of demon2036/MLLM-JAX: the token-level loss
+ * computed from logits inside TrainGRPOModule.__call__
+ * (MLLM_JAX/train_modules/__init__.py:118-180) and its gradient with respect
+ * to the logits (jax.value_and_grad at plugins/training/update/train_step.py:24).
+ * The policy part of PPOActorCriticModule.__call__
+ * (plugins/training/ppo/module.py:66-102) is the same operator with per-token
+ * advantages.  The reference has no FFI for this path (it is plain jax.numpy);
+ * these entry points are what an XLA FFI handler / ctypes stub binds instead.
+ *
+ * Conventions
+ *   - Every pointer in mllm_grpo_args is a DEVICE pointer owned by the caller.
+ *     The library allocates nothing (except where an entry point says so),
+ *     never synchronises the host, and enqueues all work on the caller's
+ *     stream (`stream` is a cudaStream_t passed as void*).
+ *   - Every entry point returns an mllm_grpo_status (0 = ok).  Nothing throws.
+ *   - Geometry: logits hold n_seqs sequences of seq_rows rows each, row r of
+ *     sequence b starts at element (b*seq_rows + r)*row_stride.  Only the first
+ *     scored_rows rows of a sequence are scored; the reference layout is
+ *     seq_rows = L, scored_rows = L-1 (logits[:, :-1, :] against
+ *     input_ids[:, 1:], train_modules/__init__.py:118-126).  A flat [N, V]
+ *     problem is n_seqs = N, seq_rows = scored_rows = 1, or any (B, T, T).
+ *   - Per-token side arrays are dense [n_seqs * scored_rows] in (b, t) order.
+ *   - Vocabulary sharding: a call sees columns
+ *     [vocab_start, vocab_start + vocab) of a vocabulary of any total size;
+ *     chosen_ids are GLOBAL ids.
+ */
+#ifndef MLLM_GRPO_H_
+#define MLLM_GRPO_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MLLM_GRPO_ABI_VERSION 1
+
+typedef enum mllm_grpo_status {
+  MLLM_GRPO_OK = 0,
+  MLLM_GRPO_ERR_NULL_POINTER = 1,   /* a required pointer is NULL */
+  MLLM_GRPO_ERR_BAD_SHAPE = 2,      /* non-positive size, scored_rows > seq_rows, row_stride < vocab ... */
+  MLLM_GRPO_ERR_BAD_ATTRIBUTE = 3,  /* temperature <= 0, negative epsilon, softcap < 0 ... */
+  MLLM_GRPO_ERR_STRUCT_SIZE = 4,    /* args->struct_size does not match this library */
+  MLLM_GRPO_ERR_ALIGNMENT = 5,      /* a side array is not 4-byte aligned / logits not 2-byte aligned */
+  MLLM_GRPO_ERR_LAUNCH = 6,         /* the CUDA runtime refused the launch (see mllm_grpo_last_cuda_error) */
+  MLLM_GRPO_ERR_UNSUPPORTED = 7,    /* combination not implemented (stated per entry point) */
+  MLLM_GRPO_ERR_TOO_LARGE = 8,      /* problem exceeds a fixed capacity of the entry point */
+  MLLM_GRPO_ERR_NO_DEVICE = 9       /* no CUDA device / wrong architecture */
+} mllm_grpo_status;
+
+/* Bits the kernels may OR into *args->device_status (an int32 in device memory,
+ * read by the host after it has synchronised the stream itself). */
+#define MLLM_GRPO_DEV_ID_CLAMPED 1   /* a chosen id fell outside [0, vocab_total) and was clamped */
+#define MLLM_GRPO_DEV_WAIT_TIMEOUT 2 /* a bounded wait on a peer flag ran out */
+
+/* One struct serves every entry point; each entry point documents the fields
+ * it reads.  Zero-initialise it, set struct_size = sizeof(mllm_grpo_args). */
+typedef struct mllm_grpo_args {
+  uint64_t struct_size;
+
+  /* ---- geometry ---- */
+  int64_t n_seqs;       /* B  > 0 */
+  int64_t seq_rows;     /* L  >= scored_rows */
+  int64_t scored_rows;  /* T  > 0 */
+  int64_t vocab;        /* columns held by this call (V, or V/k when sharded) */
+  int64_t row_stride;   /* elements between consecutive rows of logits AND dlogits, >= vocab */
+  int64_t vocab_start;  /* global id of local column 0 (0 when unsharded) */
+  int64_t vocab_total;  /* global vocabulary size; 0 means vocab_start + vocab */
+
+  /* ---- attributes: TrainGRPOModule fields, train_modules/__init__.py:89-93 ---- */
+  float temperature;    /* > 0.  lp = log_softmax(x)[c] / temperature (:124-126) */
+  float epsilon_low;    /* clip lower bound is 1 - epsilon_low  (:170) */
+  float epsilon_high;   /* clip upper bound is 1 + epsilon_high (:170) */
+  float beta;           /* weight of the k3 KL term; used only if ref_logps != NULL */
+  float softcap;        /* 0 = off; else y = softcap*tanh(x/softcap) replaces x
+                           (deprecated/MLLM_JAX/language/gemma/transformer.py:337-339) */
+  int32_t adv_per_token;/* 0: advantages is [n_seqs] (train_modules :173);
+                           1: [n_seqs*scored_rows] (ppo/module.py:87-94) */
+  int32_t flags;        /* MLLM_GRPO_FLAG_* */
+  float grad_scale;     /* upstream cotangent of the loss used when grad_scale_dev == NULL */
+  float total_valid;    /* total_valid_token_count used when total_valid_dev == NULL (:179) */
+
+  /* ---- inputs ---- */
+  const void* logits;            /* bf16 [n_seqs, seq_rows, row_stride] */
+  const int32_t* chosen_ids;     /* [B*T] global token ids (input_ids[:, 1:], :118) */
+  const float* mask;             /* [B*T] completion mask as f32 0/1 (labels[:, 1:], :120) */
+  const float* advantages;       /* [B] or [B*T] */
+  const float* old_logps;        /* [B*T] or NULL: NULL means old = stop_gradient(lp) (:161-165) */
+  const float* ref_logps;        /* [B*T] or NULL: reference-policy log-probs for the KL term */
+  const float* total_valid_dev;  /* scalar in device memory or NULL (then total_valid is used) */
+  const float* grad_scale_dev;   /* scalar in device memory or NULL (then grad_scale is used) */
+
+  /* ---- outputs of the forward; inputs of the backward ---- */
+  float* per_token_logps; /* [B*T]  lp  (returned by the reference as 'per_token_logps', :187) */
+  float* token_entropy;   /* [B*T]  H_t = -sum p log p of softmax(x/temperature) (:136-138); may be NULL */
+  float* lse;             /* [B*T]  log-sum-exp of the (soft-capped) row: residual for the backward */
+  float* grad_coef;       /* [B*T]  mask*w_t/temperature, w_t = dloss_t/dlp_t sign-flipped: residual */
+  float* loss;            /* [1]    sum_t mask_t*(-ppo_t + beta*kl_t) / total_valid (:178-180) */
+  float* loss_terms;      /* [B*T]  scratch: per-token numerators, reduced in a fixed order */
+
+  /* ---- output of the backward ---- */
+  void* dlogits;          /* bf16 [n_seqs, seq_rows, row_stride]; may alias logits (in place) */
+
+  /* ---- vocabulary-sharded path ---- */
+  float* partials;        /* [B*T, 4] (max, sumexp, sum e*y, chosen-or-0) of THIS shard */
+  const float* gathered_partials; /* [n_shards, B*T, 4]: every shard's partials (after the exchange) */
+  int32_t n_shards;
+  int32_t reserved0;
+
+  /* ---- error reporting ---- */
+  int32_t* device_status; /* optional int32 in device memory; kernels OR MLLM_GRPO_DEV_* bits into it */
+} mllm_grpo_args;
+
+#define MLLM_GRPO_FLAG_SKIP_ENTROPY 1 /* do not compute token_entropy (saves one FMA per element) */
+
+/* Forward over full rows (vocab_start = 0, vocab = vocab_total).
+ * Replaces train_modules/__init__.py:118-180 (ppo/module.py:66-102 with adv_per_token = 1).
+ * Reads logits once.  Writes per_token_logps, token_entropy (unless NULL or
+ * SKIP_ENTROPY), lse, grad_coef, loss_terms and loss. */
+int mllm_grpo_fwd(const mllm_grpo_args* args, void* stream);
+
+/* Backward: dlogits[b, r, j] = g*(softmax_j - onehot_j) (times the soft-cap
+ * derivative), g = grad_scale * grad_coef / total_valid; rows r >= scored_rows
+ * and rows whose g is 0 are written as exact zeros without reading logits.
+ * Replaces the autodiff of the region above (update/train_step.py:24).
+ * Reads lse, grad_coef, chosen_ids, logits; writes dlogits (bf16).
+ * With vocab sharding each shard calls it on its own columns; no exchange. */
+int mllm_grpo_bwd(const mllm_grpo_args* args, void* stream);
+
+/* Forward and backward in one launch, the shape of jax.value_and_grad in
+ * training_step (update/train_step.py:24): every output of mllm_grpo_fwd and
+ * of mllm_grpo_bwd.  The row is kept on chip between the two sweeps, so logits
+ * are read from HBM once.  grad_scale must be known up front (1.0 in
+ * training_step). */
+int mllm_grpo_fwd_bwd(const mllm_grpo_args* args, void* stream);
+
+/* Vocabulary-sharded forward, step 1: per-token (max, sumexp, sum e*y,
+ * chosen-logit-or-0) of this shard's columns -> partials[B*T, 4].  This is the
+ * per-shard part of the all-reduce(max)/all-reduce(sum) XLA inserts when
+ * log_softmax runs on tp-sharded logits (MLLM_JAX/utils.py:245). */
+int mllm_grpo_fwd_partials(const mllm_grpo_args* args, void* stream);
+
+/* Vocabulary-sharded forward, step 2: merge gathered_partials[n_shards, B*T, 4]
+ * and run the per-token epilogue; same outputs as mllm_grpo_fwd. */
+int mllm_grpo_combine(const mllm_grpo_args* args, void* stream);
+
+/* Forward-only log-probs and entropies (no loss, no residuals): the
+ * reference-model pass (train_modules/__init__.py:129-132) and the first PPO
+ * epoch's per_token_logps collection (plugins/training/update/ppo.py:39-43).
+ * Reads logits, chosen_ids; writes per_token_logps, token_entropy (optional), lse (optional). */
+int mllm_grpo_logprobs(const mllm_grpo_args* args, void* stream);
+
+/* Bytes of loss_terms scratch a problem of n_tokens = B*T needs. */
+int64_t mllm_grpo_workspace_bytes(int64_t n_tokens);
+
+int mllm_grpo_abi_version(void);
+const char* mllm_grpo_status_string(int status);
+/* Text of the last CUDA runtime error seen by this thread's launches ("" if none). */
+const char* mllm_grpo_last_cuda_error(void);
+/* Number of kernels the library has launched in this process (for launch accounting). */
+int64_t mllm_grpo_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLLM_GRPO_H_ */

@@ -1,0 +1,21 @@
+"""B200 (sm_100a) fused GRPO / PPO-clip token loss: a drop-in for the loss region of
+demon2036/MLLM-JAX's TrainGRPOModule (MLLM_JAX/train_modules/__init__.py:118-180).
+
+Importing the package does not need a GPU or the built library; calling an operator does.
+"""
+from ._lib import GrpoError, LIB_PATH, launch_count  # noqa: F401
+from .ops import (  # noqa: F401
+    LossConfig,
+    TokenLossProblem,
+    grpo_token_loss,
+    grpo_token_loss_flat,
+    grpo_value_and_grad,
+    token_logprobs,
+)
+from .train_module import TrainGRPOModule, per_sample_entropy, ppo_policy_terms  # noqa: F401
+
+__all__ = [
+    "GrpoError", "LIB_PATH", "LossConfig", "TokenLossProblem", "TrainGRPOModule", "grpo_token_loss",
+    "grpo_token_loss_flat", "grpo_value_and_grad", "launch_count", "per_sample_entropy", "ppo_policy_terms",
+    "token_logprobs",
+]

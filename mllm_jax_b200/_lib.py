@@ -1,0 +1,93 @@
+"""ctypes binding of `libmllm_grpo.so` (the C ABI declared in include/mllm_grpo.h).
+
+There is no CPU fallback: if the library is missing or fails to load, every
+operator raises.  Loading does not need a GPU; launching does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmllm_grpo.so"
+
+FLAG_SKIP_ENTROPY = 1
+DEV_ID_CLAMPED = 1
+DEV_WAIT_TIMEOUT = 2
+
+EXPORTS = (
+    "mllm_grpo_fwd", "mllm_grpo_bwd", "mllm_grpo_fwd_bwd", "mllm_grpo_fwd_partials", "mllm_grpo_combine",
+    "mllm_grpo_logprobs", "mllm_grpo_workspace_bytes", "mllm_grpo_abi_version", "mllm_grpo_status_string",
+    "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count",
+)
+
+
+class GrpoArgs(C.Structure):
+    """Mirror of `struct mllm_grpo_args`; field order and types must match the header."""
+
+    _fields_ = [
+        ("struct_size", C.c_uint64),
+        ("n_seqs", C.c_int64), ("seq_rows", C.c_int64), ("scored_rows", C.c_int64), ("vocab", C.c_int64),
+        ("row_stride", C.c_int64), ("vocab_start", C.c_int64), ("vocab_total", C.c_int64),
+        ("temperature", C.c_float), ("epsilon_low", C.c_float), ("epsilon_high", C.c_float), ("beta", C.c_float),
+        ("softcap", C.c_float), ("adv_per_token", C.c_int32), ("flags", C.c_int32), ("grad_scale", C.c_float),
+        ("total_valid", C.c_float),
+        ("logits", C.c_void_p), ("chosen_ids", C.c_void_p), ("mask", C.c_void_p), ("advantages", C.c_void_p),
+        ("old_logps", C.c_void_p), ("ref_logps", C.c_void_p), ("total_valid_dev", C.c_void_p),
+        ("grad_scale_dev", C.c_void_p),
+        ("per_token_logps", C.c_void_p), ("token_entropy", C.c_void_p), ("lse", C.c_void_p),
+        ("grad_coef", C.c_void_p), ("loss", C.c_void_p), ("loss_terms", C.c_void_p),
+        ("dlogits", C.c_void_p),
+        ("partials", C.c_void_p), ("gathered_partials", C.c_void_p), ("n_shards", C.c_int32),
+        ("reserved0", C.c_int32),
+        ("device_status", C.c_void_p),
+    ]
+
+
+class GrpoError(RuntimeError):
+    def __init__(self, fn: str, status: int, text: str, cuda: str = ""):
+        self.status = status
+        super().__init__(f"{fn} failed: status {status} ({text})" + (f": {cuda}" if cuda else ""))
+
+
+_lib = None
+
+
+def load():
+    """Load the library once; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m mllm_jax_b200.build` (needs nvcc). "
+            "There is no CPU fallback for the GRPO loss kernels."
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    for name in ("mllm_grpo_fwd", "mllm_grpo_bwd", "mllm_grpo_fwd_bwd", "mllm_grpo_fwd_partials",
+                 "mllm_grpo_combine", "mllm_grpo_logprobs"):
+        fn = getattr(lib, name)
+        fn.argtypes = [C.POINTER(GrpoArgs), C.c_void_p]
+        fn.restype = C.c_int
+    lib.mllm_grpo_workspace_bytes.argtypes = [C.c_int64]
+    lib.mllm_grpo_workspace_bytes.restype = C.c_int64
+    lib.mllm_grpo_abi_version.restype = C.c_int
+    lib.mllm_grpo_status_string.argtypes = [C.c_int]
+    lib.mllm_grpo_status_string.restype = C.c_char_p
+    lib.mllm_grpo_last_cuda_error.restype = C.c_char_p
+    lib.mllm_grpo_launch_count.restype = C.c_int64
+    _lib = lib
+    return lib
+
+
+def call(name: str, args: GrpoArgs, stream: int) -> None:
+    """Invoke one launcher; raise GrpoError on a non-zero status."""
+    lib = load()
+    args.struct_size = C.sizeof(GrpoArgs)
+    status = getattr(lib, name)(C.byref(args), C.c_void_p(stream))
+    if status != 0:
+        raise GrpoError(name, status, lib.mllm_grpo_status_string(status).decode(),
+                        lib.mllm_grpo_last_cuda_error().decode())
+
+
+def launch_count() -> int:
+    return int(load().mllm_grpo_launch_count())

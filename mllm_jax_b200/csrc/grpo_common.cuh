@@ -1,0 +1,201 @@
+// Shared device helpers of the fused GRPO token-loss kernels (sm_100a only).
+//
+// Notation (one scored token = one logits row):
+//   y_j  = x_j, or softcap*tanh(x_j/softcap) when the soft-cap is on
+//   M    = max_j y_j      S = sum_j e^(y_j - M)      U = sum_j e^(y_j - M) * y_j
+//   lse  = M + log S      lp = (y_c - lse)/temperature      H = lse - U/S
+// which restates MLLM_JAX/train_modules/__init__.py:124-126 (log-prob) and
+// :136-138 (entropy, without its +1e-9 guard) as streaming sums.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace grpo {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+// Finite stand-in for "no element seen yet": its product with log2(e) stays finite.
+constexpr float kNegInit = -1.0e30f;
+
+struct KernelParams {
+  // geometry
+  int64_t n_seqs, seq_rows, scored_rows, vocab, row_stride, vocab_start, vocab_total;
+  // attributes
+  float inv_temperature, clip_lo, clip_hi, beta, softcap;
+  float grad_scale, total_valid;
+  int adv_per_token;
+  // inputs
+  const __nv_bfloat16* logits;
+  const int32_t* chosen_ids;
+  const float* mask;
+  const float* advantages;
+  const float* old_logps;
+  const float* ref_logps;
+  const float* total_valid_dev;
+  const float* grad_scale_dev;
+  // outputs / residuals
+  float* per_token_logps;
+  float* token_entropy;
+  float* lse;
+  float* grad_coef;
+  float* loss;
+  float* loss_terms;
+  __nv_bfloat16* dlogits;
+  float* partials;
+  const float* gathered_partials;
+  int n_shards;
+  int32_t* device_status;
+};
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2f(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcpf(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// bf16 pair packed in one 32-bit word -> two f32 (exact: bf16 is the top half of f32).
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// Exact packed max of two bf16 pairs (one HMNMX2 per two elements).
+__device__ __forceinline__ uint32_t bf16x2_max(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// Two f32 -> packed bf16 pair, round to nearest even (lo in the low half).
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+// Soft-cap y = cap*tanh(x/cap) as cap - 2cap/(1 + e^(2x/cap)): two SFU ops, absolute
+// error ~1e-7*cap (tanh.approx would be ~5e-4 relative, too coarse for a 2e-3 log-prob bound).
+struct SoftCap {
+  float c1;    // 2*log2(e)/cap
+  float cap;
+  __device__ __forceinline__ explicit SoftCap(float cap_) : c1(2.0f * kLog2e / cap_), cap(cap_) {}
+  // r = 1/(1+e^(2x/cap)); tanh = 1-2r; 1-tanh^2 = 4r(1-r)
+  __device__ __forceinline__ float r(float x) const { return rcpf(1.0f + ex2f(x * c1)); }
+  __device__ __forceinline__ float y(float x) const { return fmaf(-2.0f * cap, r(x), cap); }
+};
+
+// Streaming accumulator of one thread.  ENT: 0 none, 1 entropy at temperature 1
+// (U shares S), 2 entropy at temperature != 1 (own S2/U2 on y/temperature).
+template <int ENT>
+struct RowAcc {
+  float m, s, u, s2, u2;
+  __device__ __forceinline__ void init() {
+    m = kNegInit;
+    s = 0.f;
+    u = 0.f;
+    s2 = 0.f;
+    u2 = 0.f;
+  }
+  // Raise the running max to mnew (>= m) and rescale the sums.
+  __device__ __forceinline__ void raise(float mnew, float inv_temp) {
+    const float d = (m - mnew) * kLog2e;
+    const float sc = ex2f(d);
+    s *= sc;
+    if (ENT == 1) u *= sc;
+    if (ENT == 2) {
+      const float sc2 = ex2f(d * inv_temp);
+      s2 *= sc2;
+      u2 *= sc2;
+    }
+    m = mnew;
+  }
+  // Add one element y given mk = m*log2e (and mk2 = mk*inv_temp for ENT == 2).
+  __device__ __forceinline__ void add(float y, float mk, float k2, float mk2) {
+    const float p = ex2f(fmaf(y, kLog2e, -mk));
+    s += p;
+    if (ENT == 1) u = fmaf(p, y, u);
+    if (ENT == 2) {
+      const float p2 = ex2f(fmaf(y, k2, -mk2));
+      s2 += p2;
+      u2 = fmaf(p2, y, u2);
+    }
+  }
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+struct RowStats {
+  float M, S, U, S2, U2;
+};
+
+// Per-token quantities produced by the epilogue.
+struct TokenOut {
+  float lp, entropy, lse, grad_coef, loss_term;
+};
+
+// Everything after the vocabulary reduction, per token n = (b, t).
+// Follows train_modules/__init__.py:161-180 (old log-probs, ratio, clip, surrogate,
+// mask) and adds beta*k3 against ref_logps.  grad_coef = mask*w/temperature with
+//   w = A*ratio*sel - beta*(1 - e^(ref - lp)),
+// sel = 1 where the unclipped branch is the active minimum (closed clip interval
+// included), so that dlogits = (grad_scale/total_valid)*grad_coef*(softmax - onehot).
+template <int ENT>
+__device__ __forceinline__ TokenOut token_epilogue(const KernelParams& p, int64_t n, int64_t b,
+                                                   const RowStats& st, float yc) {
+  TokenOut o;
+  const float lnS = logf(st.S);
+  o.lse = st.M + lnS;
+  o.lp = (yc - o.lse) * p.inv_temperature;
+  if (ENT == 1) {
+    o.entropy = o.lse - st.U / st.S;
+  } else if (ENT == 2) {
+    // softmax(y/temperature): lse2 = M/temp + ln S2, E[y/temp] = U2/(temp*S2)
+    o.entropy = st.M * p.inv_temperature + logf(st.S2) - p.inv_temperature * st.U2 / st.S2;
+  } else {
+    o.entropy = 0.f;
+  }
+  const float m = p.mask ? p.mask[n] : 1.0f;
+  const float A = p.advantages ? p.advantages[p.adv_per_token ? n : b] : 0.0f;
+  const float old = p.old_logps ? p.old_logps[n] : o.lp;
+  const float ratio = expf(o.lp - old);
+  const float clipped = fminf(fmaxf(ratio, p.clip_lo), p.clip_hi);
+  const float ppo = fminf(ratio * A, clipped * A);
+  float sel;
+  if (ratio > p.clip_hi)
+    sel = (A < 0.f) ? 1.f : 0.f;
+  else if (ratio < p.clip_lo)
+    sel = (A > 0.f) ? 1.f : 0.f;
+  else
+    sel = 1.f;
+  float term = -ppo;
+  float w = A * ratio * sel;
+  if (p.ref_logps != nullptr && p.beta != 0.f) {
+    const float d = p.ref_logps[n] - o.lp;
+    const float ed = expf(d);
+    term += p.beta * (ed - d - 1.0f);
+    w -= p.beta * (1.0f - ed);
+  }
+  o.loss_term = m * term;
+  o.grad_coef = m * w * p.inv_temperature;
+  return o;
+}
+
+}  // namespace grpo

@@ -1,0 +1,20 @@
+// Internal interface between the C-ABI layer (grpo_api.cu) and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../../include/mllm_grpo.h"
+#include "grpo_common.cuh"
+
+namespace grpo {
+
+// Bumps the process-wide count of kernels launched by this library.
+void count_launch();
+
+// mode: 0 full forward, 1 shard partials, 2 log-probs only.  ent: 0 none, 1 temperature == 1, 2 otherwise.
+cudaError_t launch_row_stats(const KernelParams& p, int mode, int ent, cudaStream_t s);
+cudaError_t launch_combine(const KernelParams& p, int ent, cudaStream_t s);
+cudaError_t launch_loss_reduce(const KernelParams& p, cudaStream_t s);
+cudaError_t launch_dlogits(const KernelParams& p, cudaStream_t s);
+
+}  // namespace grpo

@@ -1,0 +1,288 @@
+"""Python operators over the C ABI: the fused GRPO / PPO-clip token loss.
+
+These functions keep the argument names and semantics of the region they
+replace in demon2036/MLLM-JAX, `TrainGRPOModule.__call__`
+(MLLM_JAX/train_modules/__init__.py:118-180), and of its gradient with respect
+to the logits (plugins/training/update/train_step.py:24).  Tensors are torch
+CUDA tensors used only as device buffers: every computation happens inside
+`libmllm_grpo.so`, reached through raw pointers and the current CUDA stream.
+Nothing here falls back to torch math or to the CPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Union
+
+import torch
+
+from . import _lib
+from ._lib import GrpoArgs
+
+Number = Union[int, float]
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.float32).contiguous()
+
+
+@dataclass
+class LossConfig:
+    """Operator attributes; defaults are TrainGRPOModule's (train_modules/__init__.py:89-93),
+    except beta, which is 0 wherever the reference is actually configured
+    (plugins/training/config.py:40) and only acts when ref log-probs are given."""
+
+    temperature: float = 1.0
+    epsilon_low: float = 0.2
+    epsilon_high: float = 0.3
+    beta: float = 0.0
+    softcap: Optional[float] = None
+    compute_entropy: bool = True
+
+
+class TokenLossProblem:
+    """Device buffers of one call, laid out as the C ABI wants them.
+
+    logits: bf16 [B, L, V] (or a [B, L, ld] view with V leading columns used).
+    The first `scored_rows` rows of each sequence are scored; side arrays are
+    [B, scored_rows].  Keeps references so the buffers outlive the launch.
+    """
+
+    def __init__(self, logits: torch.Tensor, chosen_ids: torch.Tensor, mask: Optional[torch.Tensor],
+                 advantages: Optional[torch.Tensor], total_valid_token_count, old_logps: Optional[torch.Tensor],
+                 ref_logps: Optional[torch.Tensor], cfg: LossConfig, *, scored_rows: int,
+                 vocab: Optional[int] = None, vocab_start: int = 0, vocab_total: Optional[int] = None):
+        if not logits.is_cuda:
+            raise RuntimeError("the GRPO loss kernels run on a CUDA device only (no CPU path)")
+        if logits.dtype != torch.bfloat16:
+            raise TypeError(f"logits must be bfloat16, got {logits.dtype}")
+        if logits.dim() != 3:
+            raise ValueError(f"logits must be [B, L, V], got shape {tuple(logits.shape)}")
+        B, L, Vfull = logits.shape
+        if logits.stride(2) != 1 or logits.stride(0) != L * logits.stride(1):
+            raise ValueError("logits must have unit stride on the vocabulary and rows evenly spaced")
+        self.cfg = cfg
+        self.logits = logits
+        self.B, self.L, self.T = B, L, int(scored_rows)
+        self.V = int(vocab) if vocab is not None else Vfull
+        self.row_stride = logits.stride(1)
+        self.vocab_start = int(vocab_start)
+        self.vocab_total = int(vocab_total) if vocab_total is not None else self.vocab_start + self.V
+        N = B * self.T
+        dev = logits.device
+        self.N = N
+
+        def side(t, name, dtype):
+            if t is None:
+                return None
+            t = t.to(device=dev, dtype=dtype).contiguous()
+            if t.numel() != N:
+                raise ValueError(f"{name} must have {B}x{self.T} elements, got shape {tuple(t.shape)}")
+            return t
+
+        self.chosen_ids = side(chosen_ids, "chosen ids", torch.int32)
+        self.mask = side(mask, "mask", torch.float32)
+        self.old_logps = side(old_logps, "old_per_token_logps", torch.float32)
+        self.ref_logps = side(ref_logps, "ref_per_token_logps", torch.float32)
+        self.adv_per_token = 0
+        self.advantages = None
+        if advantages is not None:
+            adv = advantages.to(device=dev, dtype=torch.float32)
+            if adv.dim() == 2 and adv.shape[1] == 1:
+                adv = adv[:, 0]
+            if adv.numel() == B and adv.dim() == 1:
+                self.adv_per_token = 0
+            elif adv.numel() == N:
+                self.adv_per_token = 1
+            else:
+                # same complaint as plugins/training/ppo/module.py:94
+                raise ValueError(f"advantages shape {tuple(advantages.shape)} does not match per_token_logps {(B, self.T)}")
+            self.advantages = adv.contiguous()
+
+        self.total_valid_dev = None
+        self.total_valid = 1.0
+        tv = total_valid_token_count
+        if tv is None:
+            # inputs.get("total_valid_token_count", mask_loss.sum()), train_modules/__init__.py:179
+            tv = self.mask.sum() if self.mask is not None else float(N)
+        if isinstance(tv, torch.Tensor):
+            self.total_valid_dev = tv.to(device=dev, dtype=torch.float32).reshape(1)
+        else:
+            self.total_valid = float(tv)
+
+        # outputs and residuals
+        self.per_token_logps = torch.empty(B, self.T, dtype=torch.float32, device=dev)
+        self.token_entropy = torch.empty(B, self.T, dtype=torch.float32, device=dev) if cfg.compute_entropy else None
+        self.lse = torch.empty(N, dtype=torch.float32, device=dev)
+        self.grad_coef = torch.empty(N, dtype=torch.float32, device=dev)
+        self.loss = torch.empty(1, dtype=torch.float32, device=dev)
+        self.loss_terms = torch.empty(N, dtype=torch.float32, device=dev)
+        self.device_status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.dlogits: Optional[torch.Tensor] = None
+        self.grad_scale_dev: Optional[torch.Tensor] = None
+        self.grad_scale = 1.0
+        self.partials: Optional[torch.Tensor] = None
+        self.gathered: Optional[torch.Tensor] = None
+        self.n_shards = 0
+
+    def args(self) -> GrpoArgs:
+        a = GrpoArgs()
+        a.n_seqs, a.seq_rows, a.scored_rows = self.B, self.L, self.T
+        a.vocab, a.row_stride = self.V, self.row_stride
+        a.vocab_start, a.vocab_total = self.vocab_start, self.vocab_total
+        c = self.cfg
+        a.temperature, a.epsilon_low, a.epsilon_high, a.beta = c.temperature, c.epsilon_low, c.epsilon_high, c.beta
+        a.softcap = float(c.softcap) if c.softcap else 0.0
+        a.adv_per_token = self.adv_per_token
+        a.flags = 0 if c.compute_entropy else _lib.FLAG_SKIP_ENTROPY
+        a.grad_scale, a.total_valid = self.grad_scale, self.total_valid
+        a.logits = _ptr(self.logits)
+        a.chosen_ids, a.mask, a.advantages = _ptr(self.chosen_ids), _ptr(self.mask), _ptr(self.advantages)
+        a.old_logps, a.ref_logps = _ptr(self.old_logps), _ptr(self.ref_logps)
+        a.total_valid_dev, a.grad_scale_dev = _ptr(self.total_valid_dev), _ptr(self.grad_scale_dev)
+        a.per_token_logps, a.token_entropy = _ptr(self.per_token_logps), _ptr(self.token_entropy)
+        a.lse, a.grad_coef, a.loss, a.loss_terms = _ptr(self.lse), _ptr(self.grad_coef), _ptr(self.loss), _ptr(self.loss_terms)
+        a.dlogits = _ptr(self.dlogits)
+        a.partials, a.gathered_partials, a.n_shards = _ptr(self.partials), _ptr(self.gathered), self.n_shards
+        a.device_status = _ptr(self.device_status)
+        return a
+
+    def alloc_dlogits(self, inplace: bool = False) -> torch.Tensor:
+        self.dlogits = self.logits if inplace else torch.empty_like(self.logits)
+        return self.dlogits
+
+    def run(self, entry: str) -> None:
+        with torch.cuda.device(self.logits.device):
+            _lib.call(entry, self.args(), _stream())
+
+
+class _GrpoLoss(torch.autograd.Function):
+    """torch counterpart of a jax.custom_vjp around the loss: forward saves (lse, grad_coef),
+    backward receives the scalar cotangent of the loss and streams the logits once more."""
+
+    @staticmethod
+    def forward(ctx, logits, prob: TokenLossProblem, inplace_backward: bool):
+        prob.run("mllm_grpo_fwd")
+        ctx.prob = prob
+        ctx.inplace = inplace_backward
+        ctx.mark_non_differentiable(prob.per_token_logps)
+        ent = prob.token_entropy if prob.token_entropy is not None else prob.per_token_logps.new_empty(0)
+        ctx.mark_non_differentiable(ent)
+        return prob.loss.reshape(()), prob.per_token_logps, ent
+
+    @staticmethod
+    def backward(ctx, grad_loss, _g_lp, _g_ent):
+        prob: TokenLossProblem = ctx.prob
+        prob.grad_scale_dev = grad_loss.to(torch.float32).reshape(1).contiguous()
+        prob.alloc_dlogits(ctx.inplace)
+        prob.run("mllm_grpo_bwd")
+        return prob.dlogits, None, None
+
+
+def _shifted_side(input_ids: torch.Tensor, labels: torch.Tensor):
+    # chosen_ids = input_ids[:, 1:]; mask_loss = labels[:, 1:]   (train_modules/__init__.py:118-120)
+    return input_ids[:, 1:], labels[:, 1:]
+
+
+def grpo_token_loss(logits: torch.Tensor, input_ids: torch.Tensor, labels: torch.Tensor, advantages: torch.Tensor,
+                    total_valid_token_count=None, old_per_token_logps: Optional[torch.Tensor] = None,
+                    ref_per_token_logps: Optional[torch.Tensor] = None, *, temperature: float = 1.0,
+                    epsilon_low: float = 0.2, epsilon_high: float = 0.3, beta: float = 0.0,
+                    softcap: Optional[float] = None, compute_entropy: bool = True,
+                    inplace_backward: bool = False) -> dict:
+    """GRPO token loss on the reference layout.
+
+    logits [B, L, V] bf16, input_ids / labels [B, L], advantages [B] or [B, L-1],
+    old/ref log-probs [B, L-1] or None.  Row i of a sequence is scored against
+    token i+1; row L-1 is not scored and gets a zero gradient.
+    Returns {"loss": f32[] (differentiable w.r.t. logits), "per_token_logps":
+    f32[B, L-1], "token_entropy": f32[B, L-1]}.
+    """
+    cfg = LossConfig(temperature, epsilon_low, epsilon_high, beta, softcap, compute_entropy)
+    ids, mask = _shifted_side(input_ids, labels)
+    prob = TokenLossProblem(logits, ids, mask, advantages, total_valid_token_count, old_per_token_logps,
+                            ref_per_token_logps, cfg, scored_rows=logits.shape[1] - 1)
+    loss, lp, ent = _GrpoLoss.apply(logits, prob, inplace_backward)
+    return {"loss": loss, "per_token_logps": lp, "token_entropy": ent if compute_entropy else None}
+
+
+def grpo_token_loss_flat(logits: torch.Tensor, token_ids: torch.Tensor, mask: torch.Tensor,
+                         advantages: torch.Tensor, total_valid_token_count=None,
+                         old_per_token_logps: Optional[torch.Tensor] = None,
+                         ref_per_token_logps: Optional[torch.Tensor] = None, *, temperature: float = 1.0,
+                         epsilon_low: float = 0.2, epsilon_high: float = 0.3, beta: float = 0.0,
+                         softcap: Optional[float] = None, compute_entropy: bool = True,
+                         inplace_backward: bool = False) -> dict:
+    """Same loss with token ids already aligned to the rows: logits [B, T, V] (or [N, V]),
+    token_ids / mask [B, T], advantages [B] or [B, T]; every row is scored."""
+    if logits.dim() == 2:
+        logits = logits.unsqueeze(0)
+        token_ids, mask = token_ids.reshape(1, -1), mask.reshape(1, -1)
+        if advantages.numel() == logits.shape[1]:
+            advantages = advantages.reshape(1, -1)
+    cfg = LossConfig(temperature, epsilon_low, epsilon_high, beta, softcap, compute_entropy)
+    prob = TokenLossProblem(logits, token_ids, mask, advantages, total_valid_token_count, old_per_token_logps,
+                            ref_per_token_logps, cfg, scored_rows=logits.shape[1])
+    loss, lp, ent = _GrpoLoss.apply(logits, prob, inplace_backward)
+    return {"loss": loss, "per_token_logps": lp, "token_entropy": ent if compute_entropy else None}
+
+
+def grpo_value_and_grad(logits: torch.Tensor, token_ids: torch.Tensor, mask: torch.Tensor, advantages: torch.Tensor,
+                        total_valid_token_count=None, old_per_token_logps: Optional[torch.Tensor] = None,
+                        ref_per_token_logps: Optional[torch.Tensor] = None, *, shifted: bool = False,
+                        cfg: Optional[LossConfig] = None, grad_scale: float = 1.0, inplace: bool = False,
+                        dlogits: Optional[torch.Tensor] = None) -> dict:
+    """Loss and dlogits in one call (the shape of jax.value_and_grad in training_step,
+    plugins/training/update/train_step.py:24), through mllm_grpo_fwd_bwd.
+
+    shifted=True takes the reference layout (token_ids = input_ids [B, L], mask = labels [B, L]);
+    shifted=False takes aligned [B, T] arrays.  Returns loss, per_token_logps, token_entropy, dlogits.
+    """
+    cfg = cfg or LossConfig()
+    if logits.dim() == 2:
+        logits = logits.unsqueeze(0)
+        token_ids, mask = token_ids.reshape(1, -1), mask.reshape(1, -1)
+    if shifted:
+        token_ids, mask = _shifted_side(token_ids, mask)
+    T = logits.shape[1] - 1 if shifted else logits.shape[1]
+    prob = TokenLossProblem(logits, token_ids, mask, advantages, total_valid_token_count, old_per_token_logps,
+                            ref_per_token_logps, cfg, scored_rows=T)
+    prob.grad_scale = float(grad_scale)
+    if dlogits is not None:
+        if dlogits.shape != logits.shape or dlogits.stride() != logits.stride() or dlogits.dtype != torch.bfloat16:
+            raise ValueError("dlogits must match logits in shape, strides and dtype")
+        prob.dlogits = dlogits
+    else:
+        prob.alloc_dlogits(inplace)
+    prob.run("mllm_grpo_fwd_bwd")
+    return {"loss": prob.loss.reshape(()), "per_token_logps": prob.per_token_logps,
+            "token_entropy": prob.token_entropy, "dlogits": prob.dlogits, "problem": prob}
+
+
+def token_logprobs(logits: torch.Tensor, token_ids: torch.Tensor, *, shifted: bool = False, temperature: float = 1.0,
+                   softcap: Optional[float] = None, compute_entropy: bool = False) -> dict:
+    """Forward-only log-probs of the chosen tokens (one read of the logits): the reference-model
+    pass (train_modules/__init__.py:129-132) and the first PPO epoch's collection of
+    old_per_token_logps (plugins/training/update/ppo.py:39-43)."""
+    if logits.dim() == 2:
+        logits = logits.unsqueeze(0)
+        token_ids = token_ids.reshape(1, -1)
+    if shifted:
+        token_ids = token_ids[:, 1:]
+    T = logits.shape[1] - 1 if shifted else logits.shape[1]
+    cfg = LossConfig(temperature=temperature, softcap=softcap, compute_entropy=compute_entropy)
+    prob = TokenLossProblem(logits, token_ids, None, None, 1.0, None, None, cfg, scored_rows=T)
+    prob.run("mllm_grpo_logprobs")
+    return {"per_token_logps": prob.per_token_logps, "token_entropy": prob.token_entropy, "lse": prob.lse.view(-1, T)}
+
+
+def check_device_status(prob: TokenLossProblem) -> int:
+    """Synchronises and returns the MLLM_GRPO_DEV_* bits the kernels raised (0 = clean)."""
+    return int(prob.device_status.item())

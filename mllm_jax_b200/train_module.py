@@ -1,0 +1,106 @@
+"""Host-side mirror of the reference's loss modules, backed by the CUDA kernels.
+
+`TrainGRPOModule` keeps the fields, the `inputs` dict and the returned dict of
+MLLM_JAX/train_modules/__init__.py:84-192; `ppo_policy_terms` covers the policy
+part of PPOActorCriticModule.__call__ (plugins/training/ppo/module.py:66-102).
+The model is any callable `model(input_ids=..., attention_mask=...) ->
+(logits, cache)` producing bf16 CUDA logits; gradients flow into it through
+torch autograd exactly where jax.value_and_grad differentiates the reference.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Mapping, Optional
+
+import torch
+
+from .ops import grpo_token_loss
+
+
+def per_sample_entropy(token_entropy: torch.Tensor, mask_loss: torch.Tensor):
+    """`entropy` and `entropy_loss` of the reference's return dict.
+
+    entropy[b]      = sum_t H_t m_t / sum_t m_t                       (train_modules/__init__.py:141-143)
+    entropy_loss[b] = the same over tokens whose running count of valid tokens is in [4, 100]  (:148-157)
+    A sample with no valid token divides 0 by 0, as the reference does.
+    """
+    m = mask_loss.to(token_entropy.dtype)
+    avg = (token_entropy * m).sum(-1) / m.sum(-1)
+    valid = mask_loss == 1
+    cum = torch.cumsum(valid.to(torch.int32), dim=-1)
+    window = valid & (cum >= 4) & (cum <= 100)
+    w = window.to(token_entropy.dtype)
+    avg_trunc = (token_entropy * w).sum(-1) / w.sum(-1)
+    return avg, avg_trunc
+
+
+@dataclass
+class TrainGRPOModule:
+    """Drop-in for the reference module: same fields (train_modules/__init__.py:85-94).
+
+    `pad_token_id`, `num_pre_Q`, `max_lengths`, `entropy_threshold` are carried and unused, as in
+    the reference.  `ref_model`, when given with beta != 0, supplies the reference log-probs
+    of the k3 KL term (an extension: the reference computes them but drops the term, :129-132,191);
+    `inputs["ref_per_token_logps"]` may supply them directly instead.
+    """
+
+    model: Any
+    pad_token_id: float = 0
+    num_pre_Q: int = 8
+    ref_model: Any = None
+    beta: float = 0.04
+    temperature: float = 1.0
+    max_lengths: float = 2048
+    epsilon_low: float = 0.2
+    epsilon_high: float = 0.3
+    entropy_threshold: float = 0.3
+    softcap: Optional[float] = None
+
+    def __call__(self, inputs: Mapping[str, Any]) -> dict:
+        from .ops import token_logprobs
+
+        input_ids = inputs["input_ids"]
+        attention_mask = inputs["attention_mask"]
+        labels = inputs["labels"]
+        logits, _ = self.model(input_ids=input_ids, attention_mask=attention_mask)
+
+        ref_lp = inputs.get("ref_per_token_logps")
+        if ref_lp is None and self.beta != 0 and self.ref_model is not None:
+            with torch.no_grad():
+                ref_logits, _ = self.ref_model(input_ids=input_ids, attention_mask=attention_mask)
+            # reference-policy log-probs are not divided by the temperature (:130-132)
+            ref_lp = token_logprobs(ref_logits, input_ids, shifted=True, softcap=self.softcap)["per_token_logps"]
+
+        out = grpo_token_loss(
+            logits, input_ids, labels, inputs["advantages"],
+            total_valid_token_count=inputs.get("total_valid_token_count"),
+            old_per_token_logps=inputs.get("old_per_token_logps"),
+            ref_per_token_logps=ref_lp,
+            temperature=self.temperature, epsilon_low=self.epsilon_low, epsilon_high=self.epsilon_high,
+            beta=self.beta if ref_lp is not None else 0.0, softcap=self.softcap,
+        )
+        entropy, entropy_loss = per_sample_entropy(out["token_entropy"], labels[:, 1:])
+        return {
+            "loss": out["loss"],
+            "per_token_logps": out["per_token_logps"].detach(),
+            "entropy": entropy,
+            "entropy_loss": entropy_loss,
+        }
+
+
+def ppo_policy_terms(logits: torch.Tensor, inputs: Mapping[str, Any], *, temperature: float = 1.0,
+                     epsilon_low: float = 0.2, epsilon_high: float = 0.2) -> dict:
+    """Policy loss, global entropy and log-probs as PPOActorCriticModule computes them
+    (plugins/training/ppo/module.py:66-102): advantages [B], [B, 1] or [B, L-1]; entropy is one
+    masked mean over the batch with a 1e-8 guard (:77).  The value-loss tail (:104-140) is a
+    [B, L] elementwise computation on the value head and stays with the caller."""
+    labels = inputs["labels"]
+    out = grpo_token_loss(
+        logits, inputs["input_ids"], labels, inputs["advantages"],
+        total_valid_token_count=inputs.get("total_valid_token_count"),
+        old_per_token_logps=inputs.get("old_per_token_logps"),
+        temperature=temperature, epsilon_low=epsilon_low, epsilon_high=epsilon_high,
+    )
+    m = labels[:, 1:].to(torch.float32)
+    entropy = (out["token_entropy"] * m).sum() / (m.sum() + 1e-8)
+    return {"policy_loss": out["loss"], "entropy": entropy, "per_token_logps": out["per_token_logps"].detach()}

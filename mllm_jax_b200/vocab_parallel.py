@@ -1,0 +1,86 @@
+"""Vocabulary-parallel GRPO loss: each rank holds V/k columns of every logits row.
+
+This is the tp-sharded case of the reference (lm_head kernel partitioned over "tp",
+MLLM_JAX/utils.py:245), where XLA inserts an all-reduce(max) and an all-reduce(sum) around
+log_softmax (MLLM_JAX/train_modules/__init__.py:125).  Here each rank computes per-token
+partials (max, sumexp, sum e*y, chosen-or-0) with one streaming kernel, the ranks exchange
+16 bytes per token (one NCCL all-gather over NVLink), every rank merges all partials and runs
+the per-token epilogue, and the backward needs no further communication.  One process per GPU.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .ops import LossConfig, TokenLossProblem
+
+
+def shard_bounds(vocab_total: int, rank: int, world: int) -> tuple[int, int]:
+    """[start, stop) of the columns rank `rank` holds; the vocabulary must split evenly."""
+    if vocab_total % world:
+        raise ValueError(f"vocabulary of {vocab_total} does not split evenly over {world} ranks")
+    per = vocab_total // world
+    return rank * per, (rank + 1) * per
+
+
+def exchange_partials(partials: torch.Tensor, group=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All-gather the per-rank partials [N, 4] into [world, N, 4] (rank-major), on any backend."""
+    world = dist.get_world_size(group)
+    if partials.dim() != 2 or partials.shape[1] != 4:
+        raise ValueError(f"partials must be [N, 4], got {tuple(partials.shape)}")
+    if out is None:
+        out = torch.empty(world, *partials.shape, dtype=partials.dtype, device=partials.device)
+    elif out.shape != (world, *partials.shape):
+        raise ValueError("gather buffer has the wrong shape")
+    dist.all_gather_into_tensor(out.view(-1), partials.contiguous().view(-1), group=group)
+    return out
+
+
+class VocabParallelLoss:
+    """fwd+bwd of the loss on this rank's column shard.  Buffers are allocated once and reused."""
+
+    def __init__(self, vocab_total: int, cfg: Optional[LossConfig] = None, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.vocab_total = int(vocab_total)
+        self.start, self.stop = shard_bounds(self.vocab_total, self.rank, self.world)
+        self.cfg = cfg or LossConfig()
+        self._gathered = None
+        self._partials = None
+
+    def problem(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None, ref_logps=None,
+                scored_rows=None) -> TokenLossProblem:
+        T = shard_logits.shape[1] if scored_rows is None else scored_rows
+        p = TokenLossProblem(shard_logits, token_ids, mask, advantages, total_valid, old_logps, ref_logps, self.cfg,
+                             scored_rows=T, vocab=self.stop - self.start, vocab_start=self.start,
+                             vocab_total=self.vocab_total)
+        if self._partials is None or self._partials.shape[0] != p.N:
+            self._partials = torch.empty(p.N, 4, dtype=torch.float32, device=shard_logits.device)
+            self._gathered = torch.empty(self.world, p.N, 4, dtype=torch.float32, device=shard_logits.device)
+        p.partials, p.gathered, p.n_shards = self._partials, self._gathered, self.world
+        return p
+
+    def forward(self, p: TokenLossProblem) -> None:
+        p.run("mllm_grpo_fwd_partials")
+        exchange_partials(p.partials, self.group, out=p.gathered)
+        p.run("mllm_grpo_combine")
+
+    def backward(self, p: TokenLossProblem, dlogits: Optional[torch.Tensor] = None, grad_scale: float = 1.0) -> torch.Tensor:
+        p.grad_scale = float(grad_scale)
+        if dlogits is not None:
+            p.dlogits = dlogits
+        elif p.dlogits is None:
+            p.alloc_dlogits()
+        p.run("mllm_grpo_bwd")
+        return p.dlogits
+
+    def value_and_grad(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None, ref_logps=None,
+                       dlogits=None) -> dict:
+        p = self.problem(shard_logits, token_ids, mask, advantages, total_valid, old_logps, ref_logps)
+        self.forward(p)
+        d = self.backward(p, dlogits)
+        return {"loss": p.loss.reshape(()), "per_token_logps": p.per_token_logps, "token_entropy": p.token_entropy,
+                "dlogits": d, "problem": p}

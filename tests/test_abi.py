@@ -1,0 +1,114 @@
+"""The C-ABI library: loads without a GPU, exports every symbol the header declares, the ctypes
+mirror of the argument struct matches the C layout, and argument validation (which runs before
+any CUDA call) returns the documented status codes.  No compute, no GPU."""
+import ctypes as C
+import os
+import re
+import subprocess
+
+import pytest
+
+from mllm_jax_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "mllm_grpo.h")
+
+
+def _declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mllm_grpo_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    lib = _lib.load()
+    names = _declared_functions()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/mllm_grpo.h but not exported"
+    assert set(_lib.EXPORTS) <= set(names)
+    assert lib.mllm_grpo_abi_version() == 1
+
+
+def test_ctypes_struct_matches_c_layout(tmp_path):
+    """Compile a C program against the public header and compare sizeof/offsetof with the ctypes mirror."""
+    fields = [f[0] for f in _lib.GrpoArgs._fields_]
+    src = tmp_path / "layout.c"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "mllm_grpo.h"', "int main(void){",
+             'printf("%zu\\n", sizeof(mllm_grpo_args));']
+    lines += [f'printf("%zu\\n", offsetof(mllm_grpo_args, {f}));' for f in fields]
+    lines += ["return 0;}"]
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", f"-I{os.path.join(ROOT, 'include')}", str(src), "-o",
+                    str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert int(out[0]) == C.sizeof(_lib.GrpoArgs)
+    for f, off in zip(fields, out[1:]):
+        assert getattr(_lib.GrpoArgs, f).offset == int(off), f
+
+
+def _valid_args():
+    a = _lib.GrpoArgs()
+    a.struct_size = C.sizeof(_lib.GrpoArgs)
+    a.n_seqs, a.seq_rows, a.scored_rows, a.vocab, a.row_stride = 2, 4, 3, 64, 64
+    a.temperature, a.epsilon_low, a.epsilon_high = 1.0, 0.2, 0.3
+    a.total_valid, a.grad_scale = 6.0, 1.0
+    return a
+
+
+def _status(name, a):
+    return getattr(_lib.load(), name)(C.byref(a), None)
+
+
+def test_validation_status_codes(built_lib):
+    lib = _lib.load()
+    assert lib.mllm_grpo_fwd(None, None) == 1  # NULL args
+    a = _valid_args()
+    a.struct_size = 8
+    assert _status("mllm_grpo_fwd", a) == 4
+    a = _valid_args()
+    assert _status("mllm_grpo_fwd", a) == 1  # logits NULL
+    for field, value in (("n_seqs", 0), ("vocab", -1), ("scored_rows", 5), ("row_stride", 63)):
+        a = _valid_args()
+        setattr(a, field, value)
+        assert _status("mllm_grpo_fwd", a) == 2, field
+    for field, value in (("temperature", 0.0), ("epsilon_low", -0.1), ("softcap", -1.0), ("temperature", float("nan"))):
+        a = _valid_args()
+        setattr(a, field, value)
+        assert _status("mllm_grpo_bwd", a) == 3, field
+    a = _valid_args()
+    a.logits = 0x1001  # odd address: not even 2-byte aligned (validation never dereferences)
+    a.chosen_ids = a.per_token_logps = 0x1000
+    assert _status("mllm_grpo_logprobs", a) == 5
+    a = _valid_args()
+    a.n_seqs = 1 << 31
+    assert _status("mllm_grpo_logprobs", a) == 8
+    assert lib.mllm_grpo_status_string(2) == b"bad shape"
+    assert lib.mllm_grpo_workspace_bytes(1000) == 4000
+    assert lib.mllm_grpo_workspace_bytes(-5) == 0
+
+
+def test_python_wrapper_raises_on_bad_status(built_lib):
+    a = _valid_args()
+    with pytest.raises(_lib.GrpoError) as e:
+        _lib.call("mllm_grpo_fwd", a, 0)
+    assert e.value.status == 1
+
+
+def test_operators_refuse_cpu_tensors():
+    import torch
+
+    from mllm_jax_b200 import grpo_token_loss
+
+    logits = torch.zeros(1, 3, 8, dtype=torch.bfloat16)
+    ids = torch.zeros(1, 3, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="CUDA device only"):
+        grpo_token_loss(logits, ids, ids, torch.zeros(1))
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        _lib.load()

@@ -1,0 +1,360 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle on the same seeded inputs.
+
+Gates: per-token log-prob 2e-3 abs, loss 1e-4 rel, dlogits 1e-2 rel (see tests/util.py);
+entropy 5e-4 abs.  Covers ragged sizes and alignments, every optional input, the reference
+(shifted) and flat layouts, in-place backward, the fused entry point, vocabulary shards,
+the golden fixtures, and the full-size workload through row samples and row-sum properties.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import mllm_jax_b200 as G
+from mllm_jax_b200 import synth
+from oracle import grpo_oracle as O
+from tests.util import (ENT_ATOL, LP_ATOL, assert_dlogits_close, assert_loss_close, make_case, to_device)
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def run_both(logits, inputs, cuda, *, fused=False, **attrs):
+    """Oracle on CPU and kernels on the GPU for one reference-layout case."""
+    o_attrs = {k: v for k, v in attrs.items() if k != "inplace_backward"}
+    ref = O.reference_value_and_grad(logits, inputs, **o_attrs)
+    x = logits.to(cuda)
+    din = to_device(inputs, cuda)
+    if fused:
+        cfg = G.LossConfig(temperature=attrs.get("temperature", 1.0), epsilon_low=attrs.get("epsilon_low", 0.2),
+                           epsilon_high=attrs.get("epsilon_high", 0.3), beta=attrs.get("beta", 0.0),
+                           softcap=attrs.get("softcap"))
+        out = G.grpo_value_and_grad(x, din["input_ids"], din["labels"], din["advantages"],
+                                    din.get("total_valid_token_count"), din.get("old_per_token_logps"),
+                                    din.get("ref_per_token_logps"), shifted=True, cfg=cfg)
+        got = {"loss": out["loss"], "per_token_logps": out["per_token_logps"],
+               "token_entropy": out["token_entropy"], "dlogits": out["dlogits"]}
+    else:
+        xg = x.clone().requires_grad_(True)
+        out = G.grpo_token_loss(xg, din["input_ids"], din["labels"], din["advantages"],
+                                din.get("total_valid_token_count"), din.get("old_per_token_logps"),
+                                din.get("ref_per_token_logps"), **attrs)
+        out["loss"].backward()
+        got = {"loss": out["loss"].detach(), "per_token_logps": out["per_token_logps"],
+               "token_entropy": out["token_entropy"], "dlogits": xg.grad}
+    torch.cuda.synchronize()
+    return ref, got
+
+
+def check(ref, got, what=""):
+    lp_err = (got["per_token_logps"].cpu() - ref["per_token_logps"]).abs().max().item()
+    assert lp_err <= LP_ATOL, f"{what}: log-prob error {lp_err:.3e}"
+    assert_loss_close(got["loss"].item(), ref["loss"].item(), what=what)
+    if got["token_entropy"] is not None:
+        e_err = (got["token_entropy"].cpu() - ref["token_entropy"]).abs().max().item()
+        assert e_err <= ENT_ATOL, f"{what}: entropy error {e_err:.3e}"
+    assert got["dlogits"].dtype == torch.bfloat16
+    assert_dlogits_close(got["dlogits"], ref["dlogits"], what=what)
+    return lp_err
+
+
+@pytest.mark.parametrize("V", [8, 129, 1000, 4099, 32000])
+@pytest.mark.parametrize("B,L", [(1, 2), (3, 2), (2, 130)])
+def test_ragged_sizes(cuda, V, B, L):
+    if V == 32000 and L == 130:
+        L = 40
+    logits, inputs = make_case(B, L, V, seed=V + B, old="noisy", ref=True)
+    ref, got = run_both(logits, inputs, cuda, beta=0.04)
+    check(ref, got, f"V={V} B={B} L={L}")
+
+
+def test_full_vocab_rows(cuda):
+    logits, inputs = make_case(2, 9, 151936, seed=5, old="noisy", ref=True)
+    ref, got = run_both(logits, inputs, cuda, beta=0.04, epsilon_low=0.2, epsilon_high=0.2)
+    err = check(ref, got, "V=151936")
+    assert err < 2e-4  # far inside the gate on ordinary rows
+
+
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("kind", ["no_old", "wide_clip", "kl", "token_adv", "random_mask", "temp", "softcap"])
+def test_options(cuda, kind, fused):
+    kw, attrs = dict(old="noisy"), {}
+    if kind == "no_old":
+        kw = dict(old="none")
+    elif kind == "wide_clip":
+        kw = dict(old="wide")
+        attrs = dict(epsilon_low=0.1, epsilon_high=0.15)
+    elif kind == "kl":
+        kw = dict(old="wide", ref=True)
+        attrs = dict(beta=0.5)
+    elif kind == "token_adv":
+        kw = dict(old="wide", per_token_adv=True)
+    elif kind == "random_mask":
+        kw = dict(old="noisy", mask_kind="random")
+    elif kind == "temp":
+        attrs = dict(temperature=0.7)
+    elif kind == "softcap":
+        kw = dict(old="noisy", ref=True, sigma=4.0)
+        attrs = dict(softcap=30.0, beta=0.04)
+    logits, inputs = make_case(3, 11, 5003, seed=31, **kw)
+    ref, got = run_both(logits, inputs, cuda, fused=fused, **attrs)
+    check(ref, got, f"{kind} fused={fused}")
+
+
+def test_softcap_full_gemma_vocab(cuda):
+    logits, inputs = make_case(1, 4, 256000, seed=32, old="noisy", ref=True, sigma=4.0)
+    ref, got = run_both(logits, inputs, cuda, softcap=30.0, beta=0.04, epsilon_low=0.2, epsilon_high=0.2)
+    check(ref, got, "gemma softcap")
+
+
+def test_unaligned_and_strided_views(cuda):
+    """Rows that start off a 16-byte boundary and a padded row stride."""
+    B, L, V = 2, 6, 1003
+    logits, inputs = make_case(B, L, V, seed=33, old="noisy")
+    ref = O.reference_value_and_grad(logits, inputs)
+    din = to_device(inputs, cuda)
+    for offset, ld in ((1, V), (3, V + 5), (0, V + 13), (7, V + 8)):
+        buf = torch.zeros(B * L * ld + 16, dtype=torch.bfloat16, device=cuda)
+        view = buf[offset:offset + B * L * ld].view(B, L, ld)[:, :, :V]
+        view.copy_(logits.to(cuda))
+        prob = G.TokenLossProblem(view, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"],
+                                  din["total_valid_token_count"], din["old_per_token_logps"], None,
+                                  G.LossConfig(), scored_rows=L - 1, vocab=V)
+        dbuf = torch.full_like(buf, 7.0)
+        prob.dlogits = dbuf[offset:offset + B * L * ld].view(B, L, ld)[:, :, :V]
+        prob.run("mllm_grpo_fwd_bwd")
+        torch.cuda.synchronize()
+        got = {"loss": prob.loss[0], "per_token_logps": prob.per_token_logps, "token_entropy": prob.token_entropy,
+               "dlogits": prob.dlogits}
+        check(ref, got, f"offset={offset} ld={ld}")
+        # padding columns and guard elements around the output are untouched
+        full = dbuf[offset:offset + B * L * ld].view(B, L, ld)
+        assert (full[:, :, V:] == 7.0).all()
+        assert (dbuf[:offset] == 7.0).all() and (dbuf[offset + B * L * ld:] == 7.0).all()
+
+
+def test_mismatched_phase_uses_scalar_path(cuda):
+    """logits and dlogits rows at different offsets from a 16-byte boundary."""
+    B, L, V = 1, 3, 515
+    logits, inputs = make_case(B, L, V, seed=34, old="noisy")
+    ref = O.reference_value_and_grad(logits, inputs)
+    din = to_device(inputs, cuda)
+    x = logits.to(cuda)
+    prob = G.TokenLossProblem(x, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"],
+                              din["total_valid_token_count"], din["old_per_token_logps"], None, G.LossConfig(),
+                              scored_rows=L - 1)
+    dbuf = torch.zeros(B * L * V + 8, dtype=torch.bfloat16, device=cuda)
+    prob.dlogits = dbuf[3:3 + B * L * V].view(B, L, V)
+    prob.run("mllm_grpo_fwd_bwd")
+    assert_dlogits_close(prob.dlogits, ref["dlogits"], what="phase mismatch")
+
+
+def test_inplace_backward(cuda):
+    logits, inputs = make_case(2, 7, 4096, seed=35, old="wide")
+    ref = O.reference_value_and_grad(logits, inputs)
+    din = to_device(inputs, cuda)
+    x = logits.to(cuda)
+    out = G.grpo_value_and_grad(x, din["input_ids"], din["labels"], din["advantages"],
+                                din["total_valid_token_count"], din["old_per_token_logps"], shifted=True, inplace=True)
+    assert out["dlogits"].data_ptr() == x.data_ptr()
+    assert_dlogits_close(out["dlogits"], ref["dlogits"], what="in place")
+
+
+def test_flat_layout_and_upstream_cotangent(cuda):
+    """Aligned [B, T] ids; the loss is scaled before backward so grad_scale != 1 reaches the kernel."""
+    B, T, V = 4, 16, 2000
+    logits, inputs = make_case(B, T + 1, V, seed=36, old="noisy")
+    ref = O.reference_value_and_grad(logits, inputs)
+    x = logits[:, :T].contiguous().to(cuda).requires_grad_(True)
+    din = to_device(inputs, cuda)
+    out = G.grpo_token_loss_flat(x, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"],
+                                 din["total_valid_token_count"], din["old_per_token_logps"])
+    (out["loss"] * 3.0).backward()
+    assert_loss_close(out["loss"].item(), ref["loss"].item())
+    assert_dlogits_close(x.grad, 3.0 * ref["dlogits"][:, :T], what="flat")
+
+
+def test_default_total_valid_is_mask_sum(cuda):
+    logits, inputs = make_case(2, 9, 300, seed=37, old="noisy")
+    inputs.pop("total_valid_token_count")
+    ref, got = run_both(logits, inputs, cuda)
+    check(ref, got, "default Nv")
+
+
+def test_logprobs_only(cuda):
+    logits, inputs = make_case(2, 9, 7001, seed=38, old="none")
+    ref = O.reference_call(logits, inputs, temperature=1.0)
+    out = G.token_logprobs(logits.to(cuda), inputs["input_ids"].to(cuda), shifted=True, compute_entropy=True)
+    assert (out["per_token_logps"].cpu() - ref["per_token_logps"]).abs().max() <= LP_ATOL
+    assert (out["token_entropy"].cpu() - ref["token_entropy"]).abs().max() <= ENT_ATOL
+
+
+@pytest.mark.parametrize("k", [2, 4, 8])
+@pytest.mark.parametrize("softcap", [None, 30.0])
+def test_vocab_shards_on_one_gpu(cuda, k, softcap):
+    """k column shards run one after the other on one GPU, then combined: equals the oracle."""
+    B, L, V = 2, 6, 1024 * k
+    logits, inputs = make_case(B, L, V, seed=39 + k, old="wide", ref=True, sigma=4.0 if softcap else 2.0)
+    attrs = dict(beta=0.04, softcap=softcap)
+    ref = O.reference_value_and_grad(logits, inputs, **attrs)
+    din = to_device(inputs, cuda)
+    x = logits.to(cuda)
+    cfg = G.LossConfig(beta=0.04, softcap=softcap)
+    N, Vs = B * (L - 1), V // k
+    gathered = torch.empty(k, N, 4, device=cuda)
+    probs = []
+    for r in range(k):
+        shard = x[:, :, r * Vs:(r + 1) * Vs]  # a view: row stride V, columns of shard r
+        p = G.TokenLossProblem(shard, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"],
+                               din["total_valid_token_count"], din["old_per_token_logps"],
+                               din["ref_per_token_logps"], cfg, scored_rows=L - 1, vocab=Vs, vocab_start=r * Vs,
+                               vocab_total=V)
+        p.partials = gathered[r]
+        p.run("mllm_grpo_fwd_partials")
+        probs.append(p)
+    want = np.stack([O.shard_partials(logits[:, :-1, r * Vs:(r + 1) * Vs].double().numpy().reshape(N, Vs),
+                                      inputs["input_ids"][:, 1:].numpy().reshape(-1), r * Vs, softcap)
+                     for r in range(k)])
+    assert np.allclose(gathered.cpu().numpy(), want, rtol=2e-4, atol=1e-5)
+    dfull = torch.empty_like(x)
+    for r, p in enumerate(probs):
+        p.gathered, p.n_shards = gathered, k
+        p.run("mllm_grpo_combine")
+        p.dlogits = dfull[:, :, r * Vs:(r + 1) * Vs]
+        p.run("mllm_grpo_bwd")
+    torch.cuda.synchronize()
+    got = {"loss": probs[0].loss[0], "per_token_logps": probs[0].per_token_logps,
+           "token_entropy": probs[0].token_entropy, "dlogits": dfull}
+    check(ref, got, f"k={k}")
+    for p in probs[1:]:  # every shard reaches the same replicated outputs
+        assert torch.equal(p.per_token_logps, probs[0].per_token_logps)
+        assert torch.equal(p.loss, probs[0].loss)
+
+
+def test_golden_fixtures(cuda):
+    for f in sorted(os.listdir(GOLDEN)):
+        if not f.endswith(".npz"):
+            continue
+        z = np.load(os.path.join(GOLDEN, f))
+        logits = torch.from_numpy(z["logits_bf16_bits"].astype(np.int16)).view(torch.bfloat16).to(cuda)
+        kw = dict(temperature=float(z["temperature"]), epsilon_low=float(z["epsilon_low"]),
+                  epsilon_high=float(z["epsilon_high"]), beta=float(z["beta"]), softcap=float(z["softcap"]) or None)
+        old = torch.from_numpy(z["old_per_token_logps"]).to(cuda) if "old_per_token_logps" in z.files else None
+        rf = torch.from_numpy(z["ref_per_token_logps"]).to(cuda) if "ref_per_token_logps" in z.files else None
+        x = logits.clone().requires_grad_(True)
+        out = G.grpo_token_loss(x, torch.from_numpy(z["input_ids"]).to(cuda), torch.from_numpy(z["labels"]).to(cuda),
+                                torch.from_numpy(z["advantages"]).to(cuda), float(z["total_valid_token_count"]),
+                                old, rf, **kw)
+        out["loss"].backward()
+        ref = {"loss": torch.tensor(float(z["loss"])), "per_token_logps": torch.from_numpy(z["per_token_logps"]),
+               "token_entropy": torch.from_numpy(z["token_entropy"]), "dlogits": torch.from_numpy(z["dlogits"])}
+        got = {"loss": out["loss"].detach(), "per_token_logps": out["per_token_logps"],
+               "token_entropy": out["token_entropy"], "dlogits": x.grad}
+        check(ref, got, f)
+
+
+def test_module_mirror_matches_reference_dict(cuda):
+    """TrainGRPOModule(inputs) returns the reference's dict; gradients reach the model's parameters."""
+    B, L, V, H = 3, 120, 640, 32
+    g = torch.Generator().manual_seed(40)
+    hidden = torch.randn(B, L, H, generator=g)
+    weight = torch.randn(H, V, generator=g) * 0.5
+    _, inputs = make_case(B, L, V, seed=41, old="none")
+    w_gpu = weight.to(cuda).requires_grad_(True)
+
+    def model(input_ids, attention_mask):
+        return (hidden.to(cuda) @ w_gpu).to(torch.bfloat16), None
+
+    mod = G.TrainGRPOModule(model=model, pad_token_id=0, num_pre_Q=8, beta=0.0)
+    out = mod(to_device(inputs, cuda))
+    out["loss"].backward()
+    # oracle on the same bf16 logits
+    logits = (hidden.to(cuda) @ weight.to(cuda)).to(torch.bfloat16).cpu()
+    ref = O.reference_value_and_grad(logits, inputs, beta=0.0)
+    assert set(out) == {"loss", "per_token_logps", "entropy", "entropy_loss"}
+    assert_loss_close(out["loss"].item(), ref["loss"].item())
+    assert torch.allclose(out["entropy"].cpu(), ref["entropy"], atol=ENT_ATOL, equal_nan=True)
+    assert torch.allclose(out["entropy_loss"].cpu(), ref["entropy_loss"], atol=ENT_ATOL, equal_nan=True)
+    dW = hidden.reshape(-1, H).T @ ref["dlogits"].reshape(-1, V)
+    rel = (w_gpu.grad.cpu() - dW).abs().max() / dW.abs().max()
+    assert rel < 2e-2
+
+
+def test_ppo_policy_terms(cuda):
+    logits, inputs = make_case(2, 30, 900, seed=42, old="wide", per_token_adv=True)
+    ref = O.ppo_policy_call(logits, inputs)
+    out = G.ppo_policy_terms(logits.to(cuda), to_device(inputs, cuda))
+    assert_loss_close(out["policy_loss"].item(), ref["policy_loss"].item())
+    assert abs(out["entropy"].item() - ref["entropy"].item()) <= ENT_ATOL
+    with pytest.raises(ValueError):
+        G.ppo_policy_terms(logits.to(cuda), {**to_device(inputs, cuda), "advantages": torch.zeros(2, 4)})
+
+
+def test_out_of_range_ids_are_clamped_and_flagged(cuda):
+    logits, inputs = make_case(1, 4, 100, seed=43, old="none", mask_kind="ones")
+    bad = {**inputs, "input_ids": inputs["input_ids"].clone()}
+    bad["input_ids"][0, 2] = 100
+    bad["input_ids"][0, 3] = -4
+    fixed = {**inputs, "input_ids": bad["input_ids"].clamp(0, 99)}
+    ref = O.reference_call(logits, fixed)
+    din = to_device(bad, cuda)
+    prob = G.TokenLossProblem(logits.to(cuda), din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"],
+                              3.0, None, None, G.LossConfig(), scored_rows=3)
+    prob.run("mllm_grpo_fwd")
+    assert (prob.per_token_logps.cpu() - ref["per_token_logps"]).abs().max() <= LP_ATOL
+    assert G.ops.check_device_status(prob) & 1
+
+
+def test_deterministic_repeat(cuda):
+    logits, inputs = make_case(4, 33, 3001, seed=44, old="wide", ref=True)
+    x, din = logits.to(cuda), to_device(inputs, cuda)
+    outs = []
+    for _ in range(3):
+        o = G.grpo_value_and_grad(x, din["input_ids"], din["labels"], din["advantages"],
+                                  din["total_valid_token_count"], din["old_per_token_logps"],
+                                  din["ref_per_token_logps"], shifted=True, cfg=G.LossConfig(beta=0.04))
+        outs.append((o["loss"].clone(), o["dlogits"].clone()))
+    assert all(torch.equal(outs[0][0], o[0]) and torch.equal(outs[0][1], o[1]) for o in outs[1:])
+
+
+def test_full_size_workload_properties(cuda):
+    """The benchmark workload (32768 x 151936) is too big for the oracle: check sampled rows against
+    it, and size-independent properties on everything (row sums ~ 0, zero rows exactly zero,
+    loss equals the sum over sampled + unsampled rows recomputed from per-token outputs)."""
+    w = synth.CONFIGS["cfg1"]
+    data = synth.make_inputs(w, seed=0, device="cuda")
+    cfg = G.LossConfig(epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high, beta=w.beta)
+    out = G.grpo_value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
+                                data["total_valid"], data["old_logps"], data["ref_logps"], cfg=cfg)
+    torch.cuda.synchronize()
+    N, V = w.n_tokens, w.vocab
+    d = out["dlogits"].view(N, V)
+    mask = data["mask"].view(N)
+    # zero rows are exactly zero; every row sums to ~0 (bf16 rounding of V terms)
+    rs = torch.empty(N, device=cuda)
+    absmax = torch.empty(N, device=cuda)
+    for s in range(0, N, 2048):
+        blk = d[s:s + 2048].float()
+        rs[s:s + 2048] = blk.sum(1)
+        absmax[s:s + 2048] = blk.abs().amax(1)
+    assert (absmax[mask == 0] == 0).all()
+    assert (absmax[mask == 1] > 0).float().mean() > 0.99
+    assert (rs.abs() <= 0.02 * absmax + 1e-12).all()
+    # sampled rows against the closed-form oracle
+    gen = torch.Generator().manual_seed(7)
+    rows = torch.cat([torch.tensor([0, N - 1]), torch.randint(0, N, (510,), generator=gen)]).unique()
+    x = data["logits"].view(N, V)[rows.to(cuda)].double().cpu().numpy()
+    advN = data["advantages"][:, None].expand(w.n_seqs, w.seq_len).reshape(N)
+    pick = lambda t: t.reshape(N)[rows.to(cuda)].double().cpu().numpy()  # noqa: E731
+    an = O.analytic_rows(x, data["token_ids"].reshape(N)[rows.to(cuda)].long().cpu().numpy(), pick(mask), pick(advN),
+                         pick(data["old_logps"]), pick(data["ref_logps"]), data["total_valid"], beta=w.beta,
+                         epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high)
+    assert np.abs(pick(out["per_token_logps"]) - an["lp"]).max() <= LP_ATOL
+    assert np.abs(pick(out["token_entropy"]) - an["entropy_guard"]).max() <= ENT_ATOL
+    assert_dlogits_close(d[rows.to(cuda)], torch.from_numpy(an["dlogits"]), what="cfg1 sampled rows")
+    # the loss equals the fixed-order sum of the per-token terms the kernel wrote
+    terms = out["problem"].loss_terms.double().sum().item() / data["total_valid"]
+    assert_loss_close(out["loss"].item(), terms)
+    # and the sampled terms match the oracle's
+    assert np.allclose(out["problem"].loss_terms[rows.to(cuda)].cpu().numpy(), an["loss_terms"], atol=2e-3)

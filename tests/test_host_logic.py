@@ -1,0 +1,55 @@
+"""Host-side pieces that need no GPU: the per-sample entropy reductions of the module mirror,
+the synthetic workload generator, and the package surface."""
+import math
+
+import torch
+
+from mllm_jax_b200 import per_sample_entropy, synth
+from oracle import grpo_oracle as O
+from tests.util import make_case
+
+
+def test_per_sample_entropy_matches_reference_expressions():
+    logits, inputs = make_case(3, 140, 40, seed=21, old="none", mask_kind="random")
+    inputs["labels"][2] = 0
+    out = O.reference_call(logits, inputs)
+    ent, ent_loss = per_sample_entropy(out["token_entropy"], inputs["labels"][:, 1:])
+    assert torch.allclose(ent[:2], out["entropy"][:2], atol=1e-6)
+    assert torch.allclose(ent_loss[:2], out["entropy_loss"][:2], atol=1e-6)
+    assert math.isnan(ent[2].item()) and math.isnan(ent_loss[2].item())
+
+
+def test_synth_shapes_and_distributions():
+    w = synth.scaled(synth.CONFIGS["cfg0"], vocab=512, n_seqs=8, seq_len=64, len_lo=16, len_hi=64)
+    a = synth.make_inputs(w, seed=0)
+    b = synth.make_inputs(w, seed=0)
+    c = synth.make_inputs(w, seed=1)
+    assert a["logits"].shape == (8, 64, 512) and a["logits"].dtype == torch.bfloat16
+    assert torch.equal(a["logits"], b["logits"]) and not torch.equal(a["logits"], c["logits"])
+    assert abs(a["logits"].float().std().item() - 2.0) < 0.05
+    lens = a["mask"].sum(1)
+    assert lens.min() >= 16 and lens.max() <= 64
+    assert (a["mask"][:, :-1] >= a["mask"][:, 1:]).all()  # right-padded
+    assert a["total_valid"] == float(a["mask"].sum())
+    assert abs(a["advantages"].sum().item()) < 1e-4  # group-normalised
+    assert (a["old_logps"] - a["exact_logps"]).std().item() < 0.07
+    assert (a["token_ids"] >= 0).all() and (a["token_ids"] < 512).all()
+    # exact log-probs agree with the oracle
+    inputs = {"input_ids": torch.cat([a["token_ids"][:, :1], a["token_ids"]], 1),
+              "labels": torch.ones(8, 65, dtype=torch.int32), "advantages": a["advantages"]}
+    lg = torch.cat([a["logits"], a["logits"][:, :1]], 1)
+    ref = O.reference_call(lg, inputs)
+    assert torch.allclose(ref["per_token_logps"], a["exact_logps"], atol=1e-5)
+
+
+def test_group_advantages_known_answer():
+    r = torch.tensor([1.0, 0.0, 0.0, 1.0, 1.0, 1.0, 1.0, 0.0])
+    adv = synth.group_advantages(r, 8)
+    mean, std = 5 / 8, math.sqrt(5 / 8 * 3 / 8)
+    assert torch.allclose(adv, (r - mean) / (std + 1e-6), atol=1e-6)
+
+
+def test_sweep_workload_masks_half():
+    w = synth.scaled(synth.sweep_workload(4096), vocab=64)
+    a = synth.make_inputs(w)
+    assert a["mask"].mean().item() == 0.5
