@@ -154,6 +154,23 @@ int mllm_grpo_combine(const mllm_grpo_args* args, void* stream);
  * Reads logits, chosen_ids; writes per_token_logps, token_entropy (optional), lse (optional). */
 int mllm_grpo_logprobs(const mllm_grpo_args* args, void* stream);
 
+/* Forward for callers that can neither pass a scratch buffer nor allocate one (code running inside
+ * another framework's memory plan, e.g. an XLA custom-call handler that was given operands and
+ * results only, or a loop that may not touch the allocator after start-up).  This entry point has no
+ * counterpart in the reference.  Same inputs, outputs and results as mllm_grpo_fwd, except that
+ * args->loss_terms is ignored: the per-token loss terms go to a fixed array inside the library's
+ * device image (MLLM_GRPO_STATIC_SCRATCH_TOKENS floats = 4 MiB, held by every GPU that loads the
+ * library until the process exits).
+ *   - n_seqs*scored_rows > MLLM_GRPO_STATIC_SCRATCH_TOKENS returns MLLM_GRPO_ERR_TOO_LARGE.
+ *   - Calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with
+ *     that device current); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array, and it keeps the previous call's contents.  Every
+ *     entry a call reads is written by that call first, so nothing has to be cleared; but two calls
+ *     that overlap on the GPU (different streams, no ordering between them) race on it. */
+#define MLLM_GRPO_STATIC_SCRATCH_TOKENS (1 << 20)
+int mllm_grpo_fwd_static_scratch(const mllm_grpo_args* args, void* stream);
+
 /* Bytes of loss_terms scratch a problem of n_tokens = B*T needs. */
 int64_t mllm_grpo_workspace_bytes(int64_t n_tokens);
 

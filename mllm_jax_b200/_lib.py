@@ -17,7 +17,7 @@ DEV_WAIT_TIMEOUT = 2
 EXPORTS = (
     "mllm_grpo_fwd", "mllm_grpo_bwd", "mllm_grpo_fwd_bwd", "mllm_grpo_fwd_partials", "mllm_grpo_combine",
     "mllm_grpo_logprobs", "mllm_grpo_workspace_bytes", "mllm_grpo_abi_version", "mllm_grpo_status_string",
-    "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count",
+    "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count", "mllm_grpo_fwd_static_scratch",
 )
 
 
@@ -64,7 +64,7 @@ def load():
         )
     lib = C.CDLL(str(LIB_PATH))
     for name in ("mllm_grpo_fwd", "mllm_grpo_bwd", "mllm_grpo_fwd_bwd", "mllm_grpo_fwd_partials",
-                 "mllm_grpo_combine", "mllm_grpo_logprobs"):
+                 "mllm_grpo_combine", "mllm_grpo_logprobs", "mllm_grpo_fwd_static_scratch"):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(GrpoArgs), C.c_void_p]
         fn.restype = C.c_int
