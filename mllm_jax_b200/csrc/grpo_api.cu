@@ -1,7 +1,9 @@
 // C-ABI layer: argument validation, mllm_grpo_args -> KernelParams, kernel selection.
 // Every entry point is asynchronous on the caller's stream and allocates nothing.
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
+#include <string>
 
 #include "grpo_launch.h"
 
@@ -143,7 +145,37 @@ int mllm_grpo_fwd_bwd(const mllm_grpo_args* args, void* stream) {
   if (st) return st;
   if (k.vocab_start != 0 || k.vocab != k.vocab_total) return MLLM_GRPO_ERR_BAD_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaError_t e = launch_row_stats(k, 0, entropy_mode(args), s);
+  bool taken = false;
+  cudaError_t e = cudaSuccess;
+  // Implementation choice.  Default: both passes in one kernel with the second read served by L2;
+  // rows longer than ~48 KB are split over a cluster so that few rows are in flight at a time.
+  // MLLM_GRPO_FWD_BWD_MODE overrides it: "l2cluster", "l2", "cluster" (row held in distributed
+  // shared memory, TMA in and out) or "sweeps" (separate forward and backward kernels).
+  const char* mode = std::getenv("MLLM_GRPO_FWD_BWD_MODE");
+  const std::string m = mode ? mode : "auto";
+  const char* env_cl = std::getenv("MLLM_GRPO_L2_CLUSTER");
+  const char* env_th = std::getenv("MLLM_GRPO_L2_THREADS");
+  const char* env_ct = std::getenv("MLLM_GRPO_L2_CTAS");
+  const int ent = entropy_mode(args);
+  const int64_t row_bytes = k.vocab * 2;
+  if (m == "auto" || m == "l2cluster") {
+    int cl = row_bytes >= 192 * 1024 ? 8 : (row_bytes >= 96 * 1024 ? 4 : (row_bytes >= 48 * 1024 ? 2 : 1));
+    if (env_cl) cl = std::atoi(env_cl);
+    if (cl > 1) e = launch_two_pass_cluster(k, ent, cl, env_th ? std::atoi(env_th) : 128, s, &taken);
+    if (e == cudaSuccess && !taken && m == "auto")
+      e = launch_two_pass(k, ent, env_th ? std::atoi(env_th) : 512, env_ct ? std::atoi(env_ct) : 0, s, &taken);
+  } else if (m == "l2") {
+    e = launch_two_pass(k, ent, env_th ? std::atoi(env_th) : 512, env_ct ? std::atoi(env_ct) : 0, s, &taken);
+  } else if (m == "cluster") {
+    e = launch_fused(k, ent, s, &taken);
+  }
+  if (e != cudaSuccess) return fail_cuda(e);
+  if (taken) {
+    e = launch_loss_reduce(k, s);
+    if (e != cudaSuccess) return fail_cuda(e);
+    return MLLM_GRPO_OK;
+  }
+  e = launch_row_stats(k, 0, entropy_mode(args), s);
   if (e != cudaSuccess) return fail_cuda(e);
   e = launch_loss_reduce(k, s);
   if (e != cudaSuccess) return fail_cuda(e);

@@ -157,9 +157,15 @@ struct TokenOut {
 //   w = A*ratio*sel - beta*(1 - e^(ref - lp)),
 // sel = 1 where the unclipped branch is the active minimum (closed clip interval
 // included), so that dlogits = (grad_scale/total_valid)*grad_coef*(softmax - onehot).
+// Per-token side inputs of the epilogue (old == lp when no old log-probs are given).
+struct TokenSide {
+  float mask, adv, old, ref;
+  bool has_old, has_ref;
+};
+
 template <int ENT>
-__device__ __forceinline__ TokenOut token_epilogue(const KernelParams& p, int64_t n, int64_t b,
-                                                   const RowStats& st, float yc) {
+__device__ __forceinline__ TokenOut token_epilogue_core(const KernelParams& p, const RowStats& st, float yc,
+                                                        const TokenSide& sd) {
   TokenOut o;
   const float lnS = logf(st.S);
   o.lse = st.M + lnS;
@@ -172,9 +178,8 @@ __device__ __forceinline__ TokenOut token_epilogue(const KernelParams& p, int64_
   } else {
     o.entropy = 0.f;
   }
-  const float m = p.mask ? p.mask[n] : 1.0f;
-  const float A = p.advantages ? p.advantages[p.adv_per_token ? n : b] : 0.0f;
-  const float old = p.old_logps ? p.old_logps[n] : o.lp;
+  const float m = sd.mask, A = sd.adv;
+  const float old = sd.has_old ? sd.old : o.lp;
   const float ratio = expf(o.lp - old);
   const float clipped = fminf(fmaxf(ratio, p.clip_lo), p.clip_hi);
   const float ppo = fminf(ratio * A, clipped * A);
@@ -187,8 +192,8 @@ __device__ __forceinline__ TokenOut token_epilogue(const KernelParams& p, int64_
     sel = 1.f;
   float term = -ppo;
   float w = A * ratio * sel;
-  if (p.ref_logps != nullptr && p.beta != 0.f) {
-    const float d = p.ref_logps[n] - o.lp;
+  if (sd.has_ref && p.beta != 0.f) {
+    const float d = sd.ref - o.lp;
     const float ed = expf(d);
     term += p.beta * (ed - d - 1.0f);
     w -= p.beta * (1.0f - ed);
@@ -196,6 +201,23 @@ __device__ __forceinline__ TokenOut token_epilogue(const KernelParams& p, int64_
   o.loss_term = m * term;
   o.grad_coef = m * w * p.inv_temperature;
   return o;
+}
+
+__device__ __forceinline__ TokenSide load_token_side(const KernelParams& p, int64_t n, int64_t b) {
+  TokenSide sd;
+  sd.mask = p.mask ? p.mask[n] : 1.0f;
+  sd.adv = p.advantages ? p.advantages[p.adv_per_token ? n : b] : 0.0f;
+  sd.has_old = p.old_logps != nullptr;
+  sd.old = sd.has_old ? p.old_logps[n] : 0.f;
+  sd.has_ref = p.ref_logps != nullptr;
+  sd.ref = sd.has_ref ? p.ref_logps[n] : 0.f;
+  return sd;
+}
+
+template <int ENT>
+__device__ __forceinline__ TokenOut token_epilogue(const KernelParams& p, int64_t n, int64_t b,
+                                                   const RowStats& st, float yc) {
+  return token_epilogue_core<ENT>(p, st, yc, load_token_side(p, n, b));
 }
 
 }  // namespace grpo

@@ -9,6 +9,9 @@
 //   loss_reduce_kernel: fixed-order sum of the per-token loss terms / total_valid.
 //   dlogits_kernel    : one CTA per logits row; second streaming pass writing
 //                       g*(softmax - onehot) in bf16; zero rows are write-only.
+#include <cstdlib>
+
+#include "grpo_cluster.cuh"
 #include "grpo_common.cuh"
 #include "grpo_launch.h"
 
@@ -51,6 +54,46 @@ __device__ __forceinline__ void stg_stream(uint4* p, const uint4& v) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w)
                : "memory");
+}
+
+// L2 eviction-priority policies for the kernel that reads each row twice: the first read asks L2
+// to keep the line (evict_last), the second read and the gradient stores mark theirs evict_first.
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint4 ldg_hint(const uint4* p, uint64_t pol) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p), "l"(pol)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void stg_hint(uint4* p, const uint4& v, uint64_t pol) {
+  asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w), "l"(pol)
+               : "memory");
+}
+// LD: 0 read-only streaming load, 1 coherent streaming load, 2 load with an L2 policy.
+template <int LD>
+__device__ __forceinline__ uint4 ld_row(const uint4* p, uint64_t pol) {
+  if (LD == 0) return ldg_stream(p);
+  if (LD == 1) return ldg_stream_rw(p);
+  return ldg_hint(p, pol);
+}
+template <int LD>
+__device__ __forceinline__ void st_row(uint4* p, const uint4& v, uint64_t pol) {
+  if (LD == 2)
+    stg_hint(p, v, pol);
+  else
+    stg_stream(p, v);
 }
 
 template <int THREADS>
@@ -116,25 +159,15 @@ __device__ __forceinline__ void fold_scalar(RowAcc<ENT>& acc, float x, float inv
   acc.add(y, mk, k2, mk * inv_temp);
 }
 
-// MODE: 0 full forward (epilogue + residuals + loss terms), 1 shard partials, 2 log-probs only.
-template <int THREADS, int UNROLL, int ENT, bool CAP, int MODE>
-__global__ void __launch_bounds__(THREADS) row_stats_kernel(const KernelParams p) {
-  __shared__ float red[32];
+// First streaming pass over one row: every thread returns the row's (M, S, U[, S2, U2]).
+template <int THREADS, int UNROLL, int ENT, bool CAP, int LD>
+__device__ __forceinline__ RowStats row_pass1(const uint16_t* row16, int64_t V, float inv_temp, const SoftCap& sc,
+                                              float* red, uint64_t pol) {
   const int tid = threadIdx.x;
-  const int64_t n = blockIdx.x;  // scored token index
-  const int64_t b = n / p.scored_rows;
-  const int64_t t = n - b * p.scored_rows;
-  const __nv_bfloat16* row = p.logits + (b * p.seq_rows + t) * p.row_stride;
-  const int64_t V = p.vocab;
-  const float inv_temp = p.inv_temperature;
   const float k2 = kLog2e * inv_temp;
-  const SoftCap sc(CAP ? p.softcap : 1.0f);
-
   RowAcc<ENT> acc;
   acc.init();
-
-  const RowSplit sp(row, V);
-  const uint16_t* row16 = reinterpret_cast<const uint16_t*>(row);
+  const RowSplit sp(row16, V);
   if (tid < sp.head) {
     fold_scalar<ENT, CAP>(acc, __uint_as_float(uint32_t(row16[tid]) << 16), inv_temp, k2, sc);
   }
@@ -147,15 +180,14 @@ __global__ void __launch_bounds__(THREADS) row_stats_kernel(const KernelParams p
   for (; i + int64_t(UNROLL - 1) * THREADS < sp.nvec; i += int64_t(UNROLL) * THREADS) {
     uint4 v[UNROLL];
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) v[u] = ldg_stream(vec + i + int64_t(u) * THREADS);
+    for (int u = 0; u < UNROLL; ++u) v[u] = ld_row<LD>(vec + i + int64_t(u) * THREADS, pol);
     fold_vectors<ENT, CAP, UNROLL>(acc, v, inv_temp, k2, sc);
   }
   for (; i < sp.nvec; i += THREADS) {
     uint4 v[1];
-    v[0] = ldg_stream(vec + i);
+    v[0] = ld_row<LD>(vec + i, pol);
     fold_vectors<ENT, CAP, 1>(acc, v, inv_temp, k2, sc);
   }
-
   // Block reduction: common max first, then sums rescaled to it.
   RowStats st;
   st.M = block_max<THREADS>(acc.m, red);
@@ -171,21 +203,47 @@ __global__ void __launch_bounds__(THREADS) row_stats_kernel(const KernelParams p
     st.S2 = block_sum<THREADS>(acc.s2 * scl2, red);
     st.U2 = block_sum<THREADS>(acc.u2 * scl2, red);
   }
+  return st;
+}
+
+// Chosen logit of a token: global id -> local column (clamped into the vocabulary if out of range).
+template <bool CAP>
+__device__ __forceinline__ float chosen_logit(const KernelParams& p, int64_t n, const uint16_t* row16,
+                                              const SoftCap& sc, bool* mine, int64_t* cl_out) {
+  int64_t c = p.chosen_ids[n];
+  if (c < 0 || c >= p.vocab_total) {
+    c = c < 0 ? 0 : p.vocab_total - 1;
+    if (p.device_status) atomicOr(p.device_status, MLLM_GRPO_DEV_ID_CLAMPED);
+  }
+  const int64_t cl = c - p.vocab_start;
+  *cl_out = cl;
+  *mine = (cl >= 0 && cl < p.vocab);
+  float yc = 0.f;
+  if (*mine) {
+    yc = __uint_as_float(uint32_t(row16[cl]) << 16);
+    if (CAP) yc = sc.y(yc);
+  }
+  return yc;
+}
+
+// MODE: 0 full forward (epilogue + residuals + loss terms), 1 shard partials, 2 log-probs only.
+template <int THREADS, int UNROLL, int ENT, bool CAP, int MODE>
+__global__ void __launch_bounds__(THREADS) row_stats_kernel(const KernelParams p) {
+  __shared__ float red[32];
+  const int tid = threadIdx.x;
+  const int64_t n = blockIdx.x;  // scored token index
+  const int64_t b = n / p.scored_rows;
+  const int64_t t = n - b * p.scored_rows;
+  const uint16_t* row16 = reinterpret_cast<const uint16_t*>(p.logits + (b * p.seq_rows + t) * p.row_stride);
+  const int64_t V = p.vocab;
+  const float inv_temp = p.inv_temperature;
+  const SoftCap sc(CAP ? p.softcap : 1.0f);
+  const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, 0>(row16, V, inv_temp, sc, red, 0);
 
   if (tid == 0) {
-    // Chosen logit: global id -> local column (clamped into the vocabulary if out of range).
-    int64_t c = p.chosen_ids[n];
-    if (c < 0 || c >= p.vocab_total) {
-      c = c < 0 ? 0 : p.vocab_total - 1;
-      if (p.device_status) atomicOr(p.device_status, MLLM_GRPO_DEV_ID_CLAMPED);
-    }
-    const int64_t cl = c - p.vocab_start;
-    float yc = 0.f;
-    const bool mine = (cl >= 0 && cl < V);
-    if (mine) {
-      yc = __uint_as_float(uint32_t(row16[cl]) << 16);
-      if (CAP) yc = sc.y(yc);
-    }
+    bool mine;
+    int64_t cl;
+    const float yc = chosen_logit<CAP>(p, n, row16, sc, &mine, &cl);
     if (MODE == 1) {
       float4 out = make_float4(st.M, st.S, st.U, mine ? yc : 0.f);
       reinterpret_cast<float4*>(p.partials)[n] = out;
@@ -258,45 +316,27 @@ __global__ void __launch_bounds__(1024) loss_reduce_kernel(const KernelParams p)
   }
 }
 
-// Second streaming pass.  One CTA per logits row (scored or not).
-template <int THREADS, int UNROLL, bool CAP>
-__global__ void __launch_bounds__(THREADS) dlogits_kernel(const KernelParams p) {
+// Second streaming pass over one row: dlogits = g*(softmax - onehot) (times dy/dx with the soft-cap)
+// in bf16.  g == 0 writes exact zeros without reading the logits.
+template <int THREADS, int UNROLL, bool CAP, int LD>
+__device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, int64_t V, float g, float lse,
+                                          int64_t cl, const SoftCap& sc, uint64_t pol) {
   const int tid = threadIdx.x;
-  const int64_t r = blockIdx.x;  // row index over n_seqs*seq_rows
-  const int64_t b = r / p.seq_rows;
-  const int64_t t = r - b * p.seq_rows;
-  const int64_t V = p.vocab;
-  const uint16_t* x16 = reinterpret_cast<const uint16_t*>(p.logits + r * p.row_stride);
-  uint16_t* d16 = reinterpret_cast<uint16_t*>(p.dlogits + r * p.row_stride);
   const RowSplit sp(d16, V);  // the caller guarantees logits and dlogits rows share alignment
   uint4* dvec = reinterpret_cast<uint4*>(d16 + sp.head);
-
-  float g = 0.f, lse = 0.f;
-  int64_t cl = -1;
-  if (t < p.scored_rows) {
-    const int64_t n = b * p.scored_rows + t;
-    const float nv = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
-    const float gs = p.grad_scale_dev ? *p.grad_scale_dev : p.grad_scale;
-    g = p.grad_coef[n] * gs / nv;
-    lse = p.lse[n];
-    int64_t c = p.chosen_ids[n];
-    c = c < 0 ? 0 : (c >= p.vocab_total ? p.vocab_total - 1 : c);
-    cl = c - p.vocab_start;
-  }
 
   if (g == 0.f) {
     // Unscored row, masked token or zero advantage: exact zeros, logits are not read.
     if (tid < sp.head) d16[tid] = 0;
     if (tid < sp.tail) d16[sp.head + (sp.nvec << 3) + tid] = 0;
     const uint4 z = make_uint4(0, 0, 0, 0);
-    for (int64_t i = tid; i < sp.nvec; i += THREADS) stg_stream(dvec + i, z);
+    for (int64_t i = tid; i < sp.nvec; i += THREADS) st_row<LD>(dvec + i, z, pol);
     return;
   }
 
   // g*e^(y-lse) = sign(g) * 2^(y*log2e - lse*log2e + log2|g|): the scale rides in the exponent.
   const float off = lg2f(fabsf(g)) - lse * kLog2e;
   const uint32_t sgn = g < 0.f ? 0x80008000u : 0u;
-  const SoftCap sc(CAP ? p.softcap : 1.0f);
 
   auto one = [&](float x, int64_t j) -> float {  // scalar path: signed f32 result
     float d;
@@ -326,9 +366,8 @@ __global__ void __launch_bounds__(THREADS) dlogits_kernel(const KernelParams p) 
   }
 
   const uint4* xvec = reinterpret_cast<const uint4*>(x16 + sp.head);
-  // Vector that holds the chosen column (or -1), and its lane inside the vector.
+  // Vector that holds the chosen column (or -1).
   const int64_t cv = (cl >= sp.head && cl < sp.head + (sp.nvec << 3)) ? ((cl - sp.head) >> 3) : -1;
-  const int clane = int((cl - sp.head) & 7);
 
   auto do_vec = [&](const uint4& v, int64_t idx) -> uint4 {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -348,24 +387,172 @@ __global__ void __launch_bounds__(THREADS) dlogits_kernel(const KernelParams p) 
         const float c = one(bf16hi(w[j]), j0 + 2 * j + 1);
         o[j] = pack_bf16x2(a, c);
       }
-      (void)clane;
     }
     return make_uint4(o[0], o[1], o[2], o[3]);
   };
 
+  constexpr int LDX = (LD == 0) ? 1 : LD;  // never the non-coherent path: the output may alias the input
   int64_t i = tid;
   for (; i + int64_t(UNROLL - 1) * THREADS < sp.nvec; i += int64_t(UNROLL) * THREADS) {
     uint4 v[UNROLL];
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) v[u] = ldg_stream_rw(xvec + i + int64_t(u) * THREADS);
+    for (int u = 0; u < UNROLL; ++u) v[u] = ld_row<LDX>(xvec + i + int64_t(u) * THREADS, pol);
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
-      stg_stream(dvec + i + int64_t(u) * THREADS, do_vec(v[u], i + int64_t(u) * THREADS));
+      st_row<LD>(dvec + i + int64_t(u) * THREADS, do_vec(v[u], i + int64_t(u) * THREADS), pol);
   }
   for (; i < sp.nvec; i += THREADS) {
-    const uint4 v = ldg_stream_rw(xvec + i);
-    stg_stream(dvec + i, do_vec(v, i));
+    const uint4 v = ld_row<LDX>(xvec + i, pol);
+    st_row<LD>(dvec + i, do_vec(v, i), pol);
   }
+}
+
+// Backward sweep.  One CTA per logits row (scored or not).
+template <int THREADS, int UNROLL, bool CAP>
+__global__ void __launch_bounds__(THREADS) dlogits_kernel(const KernelParams p) {
+  const int64_t r = blockIdx.x;  // row index over n_seqs*seq_rows
+  const int64_t b = r / p.seq_rows;
+  const int64_t t = r - b * p.seq_rows;
+  const uint16_t* x16 = reinterpret_cast<const uint16_t*>(p.logits + r * p.row_stride);
+  uint16_t* d16 = reinterpret_cast<uint16_t*>(p.dlogits + r * p.row_stride);
+  float g = 0.f, lse = 0.f;
+  int64_t cl = -1;
+  if (t < p.scored_rows) {
+    const int64_t n = b * p.scored_rows + t;
+    const float nv = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
+    const float gs = p.grad_scale_dev ? *p.grad_scale_dev : p.grad_scale;
+    g = p.grad_coef[n] * gs / nv;
+    lse = p.lse[n];
+    int64_t c = p.chosen_ids[n];
+    c = c < 0 ? 0 : (c >= p.vocab_total ? p.vocab_total - 1 : c);
+    cl = c - p.vocab_start;
+  }
+  const SoftCap sc(CAP ? p.softcap : 1.0f);
+  row_pass2<THREADS, UNROLL, CAP, 1>(x16, d16, p.vocab, g, lse, cl, sc, 0);
+}
+
+// Forward and backward of a row by the same CTA: the row is read from HBM with an evict_last L2
+// policy, reduced, and read again right away (an L2 hit while the number of rows in flight stays
+// well inside the 126 MB L2), so the logits cross HBM once.  One CTA per logits row; CTAs per SM
+// are capped through the dynamic shared memory request.
+template <int THREADS, int UNROLL, int ENT, bool CAP>
+__global__ void __launch_bounds__(THREADS) row_two_pass_kernel(const KernelParams p) {
+  __shared__ float red[32];
+  __shared__ float bc[2];
+  const int tid = threadIdx.x;
+  const int64_t r = blockIdx.x;
+  const int64_t b = r / p.seq_rows;
+  const int64_t t = r - b * p.seq_rows;
+  const uint16_t* x16 = reinterpret_cast<const uint16_t*>(p.logits + r * p.row_stride);
+  uint16_t* d16 = reinterpret_cast<uint16_t*>(p.dlogits + r * p.row_stride);
+  const SoftCap sc(CAP ? p.softcap : 1.0f);
+  const uint64_t keep = policy_evict_last(), drop = policy_evict_first();
+  if (t >= p.scored_rows) {
+    row_pass2<THREADS, UNROLL, CAP, 2>(x16, d16, p.vocab, 0.f, 0.f, -1, sc, drop);
+    return;
+  }
+  const int64_t n = b * p.scored_rows + t;
+  const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, 2>(x16, p.vocab, p.inv_temperature, sc, red, keep);
+  int64_t cl = -1;
+  if (tid == 0) {
+    bool mine;
+    const float yc = chosen_logit<CAP>(p, n, x16, sc, &mine, &cl);
+    const TokenOut o = token_epilogue<ENT>(p, n, b, st, yc);
+    p.per_token_logps[n] = o.lp;
+    if (ENT != 0 && p.token_entropy) p.token_entropy[n] = o.entropy;
+    p.lse[n] = o.lse;
+    p.grad_coef[n] = o.grad_coef;
+    p.loss_terms[n] = o.loss_term;
+    const float nv = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
+    const float gs = p.grad_scale_dev ? *p.grad_scale_dev : p.grad_scale;
+    bc[0] = o.grad_coef * gs / nv;
+    bc[1] = o.lse;
+  }
+  __syncthreads();
+  const float g = bc[0], lse = bc[1];
+  int64_t c = p.chosen_ids[n];
+  c = c < 0 ? 0 : (c >= p.vocab_total ? p.vocab_total - 1 : c);
+  cl = c - p.vocab_start;
+  row_pass2<THREADS, UNROLL, CAP, 2>(x16, d16, p.vocab, g, lse, cl, sc, drop);
+}
+
+// The same two passes with one logits row split over a cluster of CL CTAs (CTA r takes the r-th
+// column slice).  Rows in flight drop by CL, so the bytes that pass through L2 between the first and
+// the second read of a line shrink to a few tens of MB and the second read is an L2 hit.  The slices'
+// (M, S, U, y_c) are pushed into every peer's shared memory and published by one cluster barrier.
+// Needs 16-byte aligned rows (vocab and row stride multiples of 8, aligned bases).
+template <int CL, int THREADS, int UNROLL, int ENT, bool CAP>
+__global__ void __launch_bounds__(THREADS) row_two_pass_cluster_kernel(const KernelParams p, int64_t vec_per) {
+  __shared__ float red[32];
+  __shared__ float bc[2];
+  __shared__ __align__(16) float4 slots[8];
+  const int tid = threadIdx.x;
+  const uint32_t rank = cl::cluster_rank();
+  const int64_t r = cl::cluster_id_x();
+  const int64_t b = r / p.seq_rows;
+  const int64_t t = r - b * p.seq_rows;
+  const int64_t col0 = int64_t(rank) * vec_per * 8;
+  int64_t ncol = p.vocab - col0;
+  if (ncol > vec_per * 8) ncol = vec_per * 8;
+  const uint16_t* x16 = reinterpret_cast<const uint16_t*>(p.logits + r * p.row_stride) + col0;
+  uint16_t* d16 = reinterpret_cast<uint16_t*>(p.dlogits + r * p.row_stride) + col0;
+  const SoftCap sc(CAP ? p.softcap : 1.0f);
+  const uint64_t keep = policy_evict_last(), drop = policy_evict_first();
+  if (t >= p.scored_rows) {  // the whole cluster takes this branch together
+    row_pass2<THREADS, UNROLL, CAP, 2>(x16, d16, ncol, 0.f, 0.f, -1, sc, drop);
+    return;
+  }
+  // Tell the peers this CTA is running (its shared memory exists) without blocking yet.
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  const int64_t n = b * p.scored_rows + t;
+  const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, 2>(x16, ncol, p.inv_temperature, sc, red, keep);
+  int64_t c = p.chosen_ids[n];
+  if (c < 0 || c >= p.vocab_total) {
+    c = c < 0 ? 0 : p.vocab_total - 1;
+    if (tid == 0 && rank == 0 && p.device_status) atomicOr(p.device_status, MLLM_GRPO_DEV_ID_CLAMPED);
+  }
+  const int64_t cl_local = c - p.vocab_start - col0;  // chosen column relative to this slice
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+  if (tid < CL) {
+    float yc = 0.f;
+    if (cl_local >= 0 && cl_local < ncol) {
+      yc = __uint_as_float(uint32_t(x16[cl_local]) << 16);
+      if (CAP) yc = sc.y(yc);
+    }
+    cl::st_cluster_f4(cl::map_to_cta(cl::smem_u32(&slots[rank]), tid), make_float4(st.M, st.S, st.U, yc));
+  }
+  cl::cluster_sync_all();  // release our pushes, acquire everyone else's
+  if (tid == 0) {
+    RowStats all;
+    all.M = kNegInit;
+    for (int q = 0; q < CL; ++q) all.M = fmaxf(all.M, slots[q].x);
+    all.S = 0.f;
+    all.U = 0.f;
+    all.S2 = 0.f;
+    all.U2 = 0.f;
+    float yc = 0.f;
+    for (int q = 0; q < CL; ++q) {
+      const float4 part = slots[q];
+      const float e = ex2f((part.x - all.M) * kLog2e);
+      all.S = fmaf(part.y, e, all.S);
+      all.U = fmaf(part.z, e, all.U);
+      yc += part.w;
+    }
+    const TokenOut o = token_epilogue<ENT>(p, n, b, all, yc);
+    if (rank == 0) {
+      p.per_token_logps[n] = o.lp;
+      if (ENT != 0 && p.token_entropy) p.token_entropy[n] = o.entropy;
+      p.lse[n] = o.lse;
+      p.grad_coef[n] = o.grad_coef;
+      p.loss_terms[n] = o.loss_term;
+    }
+    const float nv = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
+    const float gs = p.grad_scale_dev ? *p.grad_scale_dev : p.grad_scale;
+    bc[0] = o.grad_coef * gs / nv;
+    bc[1] = o.lse;
+  }
+  __syncthreads();
+  row_pass2<THREADS, UNROLL, CAP, 2>(x16, d16, ncol, bc[0], bc[1], cl_local, sc, drop);
 }
 
 // Any-alignment fallback for the rare case where logits and dlogits rows do not share
@@ -433,6 +620,110 @@ cudaError_t launch_stats_m(const KernelParams& p, int ent, cudaStream_t s) {
   return cap ? launch_stats_t<MODE, 2, true>(p, s) : launch_stats_t<MODE, 2, false>(p, s);
 }
 }  // namespace
+
+namespace {
+template <int THREADS, int ENT, bool CAP>
+cudaError_t launch_two_pass_t(const KernelParams& p, int ctas_per_sm, cudaStream_t s) {
+  auto kern = row_two_pass_kernel<THREADS, 4, ENT, CAP>;
+  // A dynamic shared memory request caps the resident CTAs per SM (227 KB per SM in total).
+  size_t smem = 0;
+  if (ctas_per_sm > 0) {
+    smem = size_t(220 * 1024) / size_t(ctas_per_sm) - 1024;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return e;
+    }
+  }
+  const int64_t R = p.n_seqs * p.seq_rows;
+  kern<<<static_cast<unsigned>(R), THREADS, smem, s>>>(p);
+  count_launch();
+  return cudaGetLastError();
+}
+template <int THREADS>
+cudaError_t launch_two_pass_th(const KernelParams& p, int ent, int ctas, cudaStream_t s) {
+  const bool cap = p.softcap > 0.f;
+  if (ent == 0) return cap ? launch_two_pass_t<THREADS, 0, true>(p, ctas, s) : launch_two_pass_t<THREADS, 0, false>(p, ctas, s);
+  if (ent == 1) return cap ? launch_two_pass_t<THREADS, 1, true>(p, ctas, s) : launch_two_pass_t<THREADS, 1, false>(p, ctas, s);
+  return cap ? launch_two_pass_t<THREADS, 2, true>(p, ctas, s) : launch_two_pass_t<THREADS, 2, false>(p, ctas, s);
+}
+}  // namespace
+
+namespace {
+template <int CL, int THREADS, int UNROLL, int ENT, bool CAP>
+cudaError_t launch_two_pass_cluster_t(const KernelParams& p, cudaStream_t s) {
+  const int64_t R = p.n_seqs * p.seq_rows;
+  const int64_t nvec = p.vocab / 8;
+  const int64_t per = (nvec + CL - 1) / CL;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(R * CL), 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, row_two_pass_cluster_kernel<CL, THREADS, UNROLL, ENT, CAP>, p, per);
+  count_launch();
+  return e;
+}
+template <int CL, int THREADS, int UNROLL>
+cudaError_t launch_two_pass_cluster_u(const KernelParams& p, int ent, cudaStream_t s) {
+  const bool cap = p.softcap > 0.f;
+  if (ent == 0)
+    return cap ? launch_two_pass_cluster_t<CL, THREADS, UNROLL, 0, true>(p, s)
+               : launch_two_pass_cluster_t<CL, THREADS, UNROLL, 0, false>(p, s);
+  return cap ? launch_two_pass_cluster_t<CL, THREADS, UNROLL, 1, true>(p, s)
+             : launch_two_pass_cluster_t<CL, THREADS, UNROLL, 1, false>(p, s);
+}
+template <int CL, int THREADS>
+cudaError_t launch_two_pass_cluster_c(const KernelParams& p, int ent, int unroll, cudaStream_t s) {
+  if (unroll <= 4) return launch_two_pass_cluster_u<CL, THREADS, 4>(p, ent, s);
+  return launch_two_pass_cluster_u<CL, THREADS, 8>(p, ent, s);
+}
+template <int CL>
+cudaError_t launch_two_pass_cluster_th(const KernelParams& p, int ent, int threads, int unroll, cudaStream_t s) {
+  if (threads <= 128) return launch_two_pass_cluster_c<CL, 128>(p, ent, unroll, s);
+  return launch_two_pass_cluster_c<CL, 256>(p, ent, unroll, s);
+}
+}  // namespace
+
+// Two passes per row with the row split over a cluster.  *taken is false (nothing launched) unless
+// rows are 16-byte aligned in both buffers, every slice is non-empty and the entropy mode is 0 or 1.
+cudaError_t launch_two_pass_cluster(const KernelParams& p, int ent, int cluster, int threads, cudaStream_t s,
+                                    bool* taken) {
+  *taken = false;
+  if (ent == 2) return cudaSuccess;
+  if ((p.vocab & 7) || (p.row_stride & 7)) return cudaSuccess;
+  if ((reinterpret_cast<uintptr_t>(p.logits) & 15) || (reinterpret_cast<uintptr_t>(p.dlogits) & 15)) return cudaSuccess;
+  const int64_t nvec = p.vocab / 8;
+  if (cluster != 2 && cluster != 4 && cluster != 8) return cudaSuccess;
+  const int64_t per = (nvec + cluster - 1) / cluster;
+  if (nvec - (cluster - 1) * per <= 0) return cudaSuccess;
+  if (p.n_seqs * p.seq_rows * cluster >= (int64_t(1) << 31)) return cudaSuccess;
+  *taken = true;
+  const char* un = std::getenv("MLLM_GRPO_L2_UNROLL");
+  const int unroll = un ? std::atoi(un) : 8;
+  switch (cluster) {
+    case 2: return launch_two_pass_cluster_th<2>(p, ent, threads, unroll, s);
+    case 4: return launch_two_pass_cluster_th<4>(p, ent, threads, unroll, s);
+    default: return launch_two_pass_cluster_th<8>(p, ent, threads, unroll, s);
+  }
+}
+
+// Single-kernel forward+backward that relies on L2 for the second read.  *taken is false when
+// logits and dlogits rows do not share their 16-byte phase (the caller then runs the two sweeps).
+cudaError_t launch_two_pass(const KernelParams& p, int ent, int threads, int ctas_per_sm, cudaStream_t s,
+                            bool* taken) {
+  const uintptr_t ax = reinterpret_cast<uintptr_t>(p.logits), ad = reinterpret_cast<uintptr_t>(p.dlogits);
+  *taken = ((ax ^ ad) & 15) == 0;
+  if (!*taken) return cudaSuccess;
+  if (threads >= 1024) return launch_two_pass_th<1024>(p, ent, ctas_per_sm, s);
+  return launch_two_pass_th<512>(p, ent, ctas_per_sm, s);
+}
 
 cudaError_t launch_row_stats(const KernelParams& p, int mode, int ent, cudaStream_t s) {
   if (mode == 0) return launch_stats_m<0>(p, ent, s);
