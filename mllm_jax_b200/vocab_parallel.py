@@ -27,9 +27,9 @@ def shard_bounds(vocab_total: int, rank: int, world: int) -> tuple[int, int]:
 
 def exchange_partials(partials: torch.Tensor, group=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """All-gather the per-rank partials [N, 4] into [world, N, 4] (rank-major), on any backend."""
-    world = dist.get_world_size(group)
     if partials.dim() != 2 or partials.shape[1] != 4:
         raise ValueError(f"partials must be [N, 4], got {tuple(partials.shape)}")
+    world = dist.get_world_size(group)
     if out is None:
         out = torch.empty(world, *partials.shape, dtype=partials.dtype, device=partials.device)
     elif out.shape != (world, *partials.shape):
