@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--vp-mode", default="fused", choices=["fused", "nccl"],
+                    help="N>1: exchange inside the kernel over peer stores, or three kernels + NCCL all-gather")
     return ap.parse_args()
 
 
@@ -190,10 +192,13 @@ def main():
         data["ref_logps"] = lp + (data["ref_logps"] - data["exact_logps"])
         dlogits = torch.empty_like(data["logits"])
 
+        vp_call = vp.value_and_grad_fused if args.vp_mode == "fused" else vp.value_and_grad
+
         def step():
-            return vp.value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
-                                     data["total_valid"], data["old_logps"], data["ref_logps"], dlogits=dlogits)
-        parallelism = f"vocab-parallel tp{world}"
+            return vp_call(data["logits"], data["token_ids"], data["mask"], data["advantages"],
+                           data["total_valid"], data["old_logps"], data["ref_logps"], dlogits=dlogits)
+        parallelism = f"vocab-parallel tp{world}, exchange: " + (
+            "peer stores inside the kernel" if args.vp_mode == "fused" else "NCCL all-gather between kernels")
 
     def barrier():
         if dist is not None:

@@ -37,7 +37,8 @@
 extern "C" {
 #endif
 
-#define MLLM_GRPO_ABI_VERSION 1
+#define MLLM_GRPO_ABI_VERSION 2
+#define MLLM_GRPO_MAX_SHARDS 8
 
 typedef enum mllm_grpo_status {
   MLLM_GRPO_OK = 0,
@@ -109,10 +110,17 @@ typedef struct mllm_grpo_args {
   float* partials;        /* [B*T, 4] (max, sumexp, sum e*y, chosen-or-0) of THIS shard */
   const float* gathered_partials; /* [n_shards, B*T, 4]: every shard's partials (after the exchange) */
   int32_t n_shards;
-  int32_t reserved0;
+  int32_t shard_rank;     /* this call's shard index in [0, n_shards) (peer-exchange entry point only) */
 
   /* ---- error reporting ---- */
   int32_t* device_status; /* optional int32 in device memory; kernels OR MLLM_GRPO_DEV_* bits into it */
+
+  /* ---- peer exchange of mllm_grpo_fwd_bwd_sharded ---- */
+  void* peer_exchange[MLLM_GRPO_MAX_SHARDS]; /* peer_exchange[q]: address, valid on THIS device, of rank q's
+                                                exchange buffer (mllm_grpo_exchange_bytes each, zeroed once);
+                                                entry shard_rank is this rank's own buffer */
+  int32_t exchange_epoch; /* > 0, the same on every rank, +1 on every call that uses the buffers */
+  int32_t reserved1;
 } mllm_grpo_args;
 
 #define MLLM_GRPO_FLAG_SKIP_ENTROPY 1 /* do not compute token_entropy (saves one FMA per element) */
@@ -147,6 +155,24 @@ int mllm_grpo_fwd_partials(const mllm_grpo_args* args, void* stream);
 /* Vocabulary-sharded forward, step 2: merge gathered_partials[n_shards, B*T, 4]
  * and run the per-token epilogue; same outputs as mllm_grpo_fwd. */
 int mllm_grpo_combine(const mllm_grpo_args* args, void* stream);
+
+/* Vocabulary-sharded forward AND backward in one kernel per GPU, with the exchange inside it.
+ * Each rank (one process per GPU) calls it on its own column shard at the same time.  A CTA
+ * streams its row shard once, pushes (max, sumexp, sum e*y, chosen-or-0) with plain peer stores
+ * over NVLink into every rank's exchange buffer followed by a release flag, waits (bounded) for
+ * the other ranks' flags in its OWN buffer, merges, runs the per-token epilogue and streams the
+ * row shard a second time (an L2 hit) to write its dlogits columns.  This is the fused form of
+ * mllm_grpo_fwd_partials -> all-gather -> mllm_grpo_combine -> mllm_grpo_bwd, i.e. of the
+ * all-reduce(max)/all-reduce(sum) XLA inserts for tp-sharded logits (MLLM_JAX/utils.py:245).
+ * Every output of mllm_grpo_fwd is replicated on every rank.  Needs temperature == 1 when the
+ * entropy is requested, n_shards <= MLLM_GRPO_MAX_SHARDS, peer access enabled between the
+ * devices, and the same exchange_epoch on all ranks (buffers are double-buffered by its parity,
+ * so consecutive calls need no barrier between them).  A rank whose peers never arrive gives up
+ * after a bounded wait and sets MLLM_GRPO_DEV_WAIT_TIMEOUT in *device_status. */
+int mllm_grpo_fwd_bwd_sharded(const mllm_grpo_args* args, void* stream);
+
+/* Bytes of one rank's exchange buffer for n_tokens = B*T and n_shards ranks. */
+int64_t mllm_grpo_exchange_bytes(int64_t n_tokens, int32_t n_shards);
 
 /* Forward-only log-probs and entropies (no loss, no residuals): the
  * reference-model pass (train_modules/__init__.py:129-132) and the first PPO

@@ -18,6 +18,7 @@ EXPORTS = (
     "mllm_grpo_fwd", "mllm_grpo_bwd", "mllm_grpo_fwd_bwd", "mllm_grpo_fwd_partials", "mllm_grpo_combine",
     "mllm_grpo_logprobs", "mllm_grpo_workspace_bytes", "mllm_grpo_abi_version", "mllm_grpo_status_string",
     "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count", "mllm_grpo_fwd_static_scratch",
+    "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_exchange_bytes",
 )
 
 
@@ -38,8 +39,9 @@ class GrpoArgs(C.Structure):
         ("grad_coef", C.c_void_p), ("loss", C.c_void_p), ("loss_terms", C.c_void_p),
         ("dlogits", C.c_void_p),
         ("partials", C.c_void_p), ("gathered_partials", C.c_void_p), ("n_shards", C.c_int32),
-        ("reserved0", C.c_int32),
+        ("shard_rank", C.c_int32),
         ("device_status", C.c_void_p),
+        ("peer_exchange", C.c_void_p * 8), ("exchange_epoch", C.c_int32), ("reserved1", C.c_int32),
     ]
 
 
@@ -64,12 +66,15 @@ def load():
         )
     lib = C.CDLL(str(LIB_PATH))
     for name in ("mllm_grpo_fwd", "mllm_grpo_bwd", "mllm_grpo_fwd_bwd", "mllm_grpo_fwd_partials",
-                 "mllm_grpo_combine", "mllm_grpo_logprobs", "mllm_grpo_fwd_static_scratch"):
+                 "mllm_grpo_combine", "mllm_grpo_logprobs", "mllm_grpo_fwd_static_scratch",
+                 "mllm_grpo_fwd_bwd_sharded"):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(GrpoArgs), C.c_void_p]
         fn.restype = C.c_int
     lib.mllm_grpo_workspace_bytes.argtypes = [C.c_int64]
     lib.mllm_grpo_workspace_bytes.restype = C.c_int64
+    lib.mllm_grpo_exchange_bytes.argtypes = [C.c_int64, C.c_int32]
+    lib.mllm_grpo_exchange_bytes.restype = C.c_int64
     lib.mllm_grpo_abi_version.restype = C.c_int
     lib.mllm_grpo_status_string.argtypes = [C.c_int]
     lib.mllm_grpo_status_string.restype = C.c_char_p

@@ -102,6 +102,12 @@ static int validate(const mllm_grpo_args* a, unsigned need, KernelParams* k) {
   k->gathered_partials = a->gathered_partials;
   k->n_shards = a->n_shards;
   k->device_status = a->device_status;
+  k->shard_rank = a->shard_rank;
+  k->exchange_epoch = a->exchange_epoch;
+  for (int q = 0; q < MLLM_GRPO_MAX_SHARDS; ++q) {
+    k->peer_data[q] = nullptr;
+    k->peer_flags[q] = nullptr;
+  }
   return MLLM_GRPO_OK;
 }
 
@@ -204,6 +210,40 @@ int mllm_grpo_combine(const mllm_grpo_args* args, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e = launch_combine(k, ent, s);
   if (e != cudaSuccess) return fail_cuda(e);
+  e = launch_loss_reduce(k, s);
+  if (e != cudaSuccess) return fail_cuda(e);
+  return MLLM_GRPO_OK;
+}
+
+int64_t mllm_grpo_exchange_bytes(int64_t n_tokens, int32_t n_shards) {
+  if (n_tokens <= 0 || n_shards <= 0 || n_shards > MLLM_GRPO_MAX_SHARDS) return 0;
+  // two epoch parities x n_shards senders x n_tokens x (float4 partial + int32 flag)
+  return int64_t(2) * n_shards * n_tokens * int64_t(sizeof(float4) + sizeof(int32_t));
+}
+
+int mllm_grpo_fwd_bwd_sharded(const mllm_grpo_args* args, void* stream) {
+  KernelParams k;
+  int st = validate(args, kLogits | kIds | kEpilogueIn | kEpilogueOut | kDlogits, &k);
+  if (st) return st;
+  if (args->n_shards <= 0 || args->n_shards > MLLM_GRPO_MAX_SHARDS) return MLLM_GRPO_ERR_TOO_LARGE;
+  if (args->shard_rank < 0 || args->shard_rank >= args->n_shards || args->exchange_epoch <= 0)
+    return MLLM_GRPO_ERR_BAD_ATTRIBUTE;
+  const int ent = entropy_mode(args);
+  if (ent == 2) return MLLM_GRPO_ERR_UNSUPPORTED;  // sharded entropy needs temperature 1
+  const int64_t N = k.n_seqs * k.scored_rows;
+  for (int q = 0; q < args->n_shards; ++q) {
+    if (args->peer_exchange[q] == nullptr) return MLLM_GRPO_ERR_NULL_POINTER;
+    if (!aligned(args->peer_exchange[q], 16)) return MLLM_GRPO_ERR_ALIGNMENT;
+    k.peer_data[q] = static_cast<float4*>(args->peer_exchange[q]);
+    k.peer_flags[q] = reinterpret_cast<int*>(k.peer_data[q] + int64_t(2) * args->n_shards * N);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const char* env_th = std::getenv("MLLM_GRPO_SHARDED_THREADS");
+  const int threads = env_th ? std::atoi(env_th) : (k.vocab * 2 >= 128 * 1024 ? 512 : 256);
+  bool taken = false;
+  cudaError_t e = launch_two_pass_sharded(k, ent, threads, s, &taken);
+  if (e != cudaSuccess) return fail_cuda(e);
+  if (!taken) return MLLM_GRPO_ERR_ALIGNMENT;  // logits and dlogits rows must share their 16-byte phase
   e = launch_loss_reduce(k, s);
   if (e != cudaSuccess) return fail_cuda(e);
   return MLLM_GRPO_OK;

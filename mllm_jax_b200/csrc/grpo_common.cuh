@@ -47,6 +47,11 @@ struct KernelParams {
   const float* gathered_partials;
   int n_shards;
   int32_t* device_status;
+  // peer exchange (mllm_grpo_fwd_bwd_sharded): rank q's buffer as seen from this device
+  float4* peer_data[8];
+  int* peer_flags[8];
+  int shard_rank;
+  int exchange_epoch;
 };
 
 __device__ __forceinline__ float ex2f(float x) {

@@ -14,217 +14,9 @@
 #include "grpo_cluster.cuh"
 #include "grpo_common.cuh"
 #include "grpo_launch.h"
+#include "grpo_rowpass.cuh"
 
 namespace grpo {
-
-// ---------------------------------------------------------------------------------------------
-// Row geometry: split a row of V bf16 starting at `row` into a scalar head (until the first
-// 16-byte boundary), nvec aligned 8-element vectors and a scalar tail.
-// ---------------------------------------------------------------------------------------------
-struct RowSplit {
-  int head, tail;
-  int64_t nvec;
-  __device__ __forceinline__ RowSplit(const void* row, int64_t V) {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(row);
-    int64_t h = ((16 - (a & 15)) & 15) >> 1;
-    if (h > V) h = V;
-    head = static_cast<int>(h);
-    nvec = (V - h) >> 3;
-    tail = static_cast<int>(V - h - (nvec << 3));
-  }
-};
-
-__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-// Coherent variant for the backward pass, whose output may alias its input.
-__device__ __forceinline__ uint4 ldg_stream_rw(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ void stg_stream(uint4* p, const uint4& v) {
-  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
-
-// L2 eviction-priority policies for the kernel that reads each row twice: the first read asks L2
-// to keep the line (evict_last), the second read and the gradient stores mark theirs evict_first.
-__device__ __forceinline__ uint64_t policy_evict_last() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-__device__ __forceinline__ uint64_t policy_evict_first() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-__device__ __forceinline__ uint4 ldg_hint(const uint4* p, uint64_t pol) {
-  uint4 v;
-  asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p), "l"(pol)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ void stg_hint(uint4* p, const uint4& v, uint64_t pol) {
-  asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w), "l"(pol)
-               : "memory");
-}
-// LD: 0 read-only streaming load, 1 coherent streaming load, 2 load with an L2 policy.
-template <int LD>
-__device__ __forceinline__ uint4 ld_row(const uint4* p, uint64_t pol) {
-  if (LD == 0) return ldg_stream(p);
-  if (LD == 1) return ldg_stream_rw(p);
-  return ldg_hint(p, pol);
-}
-template <int LD>
-__device__ __forceinline__ void st_row(uint4* p, const uint4& v, uint64_t pol) {
-  if (LD == 2)
-    stg_hint(p, v, pol);
-  else
-    stg_stream(p, v);
-}
-
-template <int THREADS>
-__device__ __forceinline__ float block_max(float v, float* red) {
-  v = warp_max(v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  __syncthreads();  // protect `red` from the previous use
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float r = (lane < THREADS / 32) ? red[lane] : kNegInit;
-  return warp_max(r);
-}
-template <int THREADS>
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  __syncthreads();
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float r = (lane < THREADS / 32) ? red[lane] : 0.f;
-  return warp_sum(r);
-}
-
-// Fold a batch of NV vectors into the accumulator.
-template <int ENT, bool CAP, int NV>
-__device__ __forceinline__ void fold_vectors(RowAcc<ENT>& acc, const uint4 (&v)[NV], float inv_temp,
-                                             float k2, const SoftCap& sc) {
-  uint32_t mx2 = v[0].x;
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    if (i) mx2 = bf16x2_max(mx2, v[i].x);
-    mx2 = bf16x2_max(mx2, v[i].y);
-    mx2 = bf16x2_max(mx2, v[i].z);
-    mx2 = bf16x2_max(mx2, v[i].w);
-  }
-  float mx = fmaxf(bf16lo(mx2), bf16hi(mx2));
-  if (CAP) mx = sc.y(mx);  // tanh is monotonic: max of capped values = capped max
-  if (mx > acc.m) acc.raise(mx, inv_temp);
-  const float mk = acc.m * kLog2e;
-  const float mk2 = mk * inv_temp;
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float a = bf16lo(w[j]), b = bf16hi(w[j]);
-      if (CAP) {
-        a = sc.y(a);
-        b = sc.y(b);
-      }
-      acc.add(a, mk, k2, mk2);
-      acc.add(b, mk, k2, mk2);
-    }
-  }
-}
-
-template <int ENT, bool CAP>
-__device__ __forceinline__ void fold_scalar(RowAcc<ENT>& acc, float x, float inv_temp, float k2,
-                                            const SoftCap& sc) {
-  const float y = CAP ? sc.y(x) : x;
-  if (y > acc.m) acc.raise(y, inv_temp);
-  const float mk = acc.m * kLog2e;
-  acc.add(y, mk, k2, mk * inv_temp);
-}
-
-// First streaming pass over one row: every thread returns the row's (M, S, U[, S2, U2]).
-template <int THREADS, int UNROLL, int ENT, bool CAP, int LD>
-__device__ __forceinline__ RowStats row_pass1(const uint16_t* row16, int64_t V, float inv_temp, const SoftCap& sc,
-                                              float* red, uint64_t pol) {
-  const int tid = threadIdx.x;
-  const float k2 = kLog2e * inv_temp;
-  RowAcc<ENT> acc;
-  acc.init();
-  const RowSplit sp(row16, V);
-  if (tid < sp.head) {
-    fold_scalar<ENT, CAP>(acc, __uint_as_float(uint32_t(row16[tid]) << 16), inv_temp, k2, sc);
-  }
-  if (tid < sp.tail) {
-    const int64_t j = sp.head + (sp.nvec << 3) + tid;
-    fold_scalar<ENT, CAP>(acc, __uint_as_float(uint32_t(row16[j]) << 16), inv_temp, k2, sc);
-  }
-  const uint4* vec = reinterpret_cast<const uint4*>(row16 + sp.head);
-  int64_t i = tid;
-  for (; i + int64_t(UNROLL - 1) * THREADS < sp.nvec; i += int64_t(UNROLL) * THREADS) {
-    uint4 v[UNROLL];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) v[u] = ld_row<LD>(vec + i + int64_t(u) * THREADS, pol);
-    fold_vectors<ENT, CAP, UNROLL>(acc, v, inv_temp, k2, sc);
-  }
-  for (; i < sp.nvec; i += THREADS) {
-    uint4 v[1];
-    v[0] = ld_row<LD>(vec + i, pol);
-    fold_vectors<ENT, CAP, 1>(acc, v, inv_temp, k2, sc);
-  }
-  // Block reduction: common max first, then sums rescaled to it.
-  RowStats st;
-  st.M = block_max<THREADS>(acc.m, red);
-  const float d = (acc.m - st.M) * kLog2e;
-  const float scl = ex2f(d);
-  st.S = block_sum<THREADS>(acc.s * scl, red);
-  st.U = 0.f;
-  st.S2 = 0.f;
-  st.U2 = 0.f;
-  if (ENT == 1) st.U = block_sum<THREADS>(acc.u * scl, red);
-  if (ENT == 2) {
-    const float scl2 = ex2f(d * inv_temp);
-    st.S2 = block_sum<THREADS>(acc.s2 * scl2, red);
-    st.U2 = block_sum<THREADS>(acc.u2 * scl2, red);
-  }
-  return st;
-}
-
-// Chosen logit of a token: global id -> local column (clamped into the vocabulary if out of range).
-template <bool CAP>
-__device__ __forceinline__ float chosen_logit(const KernelParams& p, int64_t n, const uint16_t* row16,
-                                              const SoftCap& sc, bool* mine, int64_t* cl_out) {
-  int64_t c = p.chosen_ids[n];
-  if (c < 0 || c >= p.vocab_total) {
-    c = c < 0 ? 0 : p.vocab_total - 1;
-    if (p.device_status) atomicOr(p.device_status, MLLM_GRPO_DEV_ID_CLAMPED);
-  }
-  const int64_t cl = c - p.vocab_start;
-  *cl_out = cl;
-  *mine = (cl >= 0 && cl < p.vocab);
-  float yc = 0.f;
-  if (*mine) {
-    yc = __uint_as_float(uint32_t(row16[cl]) << 16);
-    if (CAP) yc = sc.y(yc);
-  }
-  return yc;
-}
 
 // MODE: 0 full forward (epilogue + residuals + loss terms), 1 shard partials, 2 log-probs only.
 template <int THREADS, int UNROLL, int ENT, bool CAP, int MODE>
@@ -313,97 +105,6 @@ __global__ void __launch_bounds__(1024) loss_reduce_kernel(const KernelParams p)
   if (threadIdx.x == 0) {
     const float nv = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
     *p.loss = float(part[0] / double(nv));
-  }
-}
-
-// Second streaming pass over one row: dlogits = g*(softmax - onehot) (times dy/dx with the soft-cap)
-// in bf16.  g == 0 writes exact zeros without reading the logits.
-template <int THREADS, int UNROLL, bool CAP, int LD>
-__device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, int64_t V, float g, float lse,
-                                          int64_t cl, const SoftCap& sc, uint64_t pol) {
-  const int tid = threadIdx.x;
-  const RowSplit sp(d16, V);  // the caller guarantees logits and dlogits rows share alignment
-  uint4* dvec = reinterpret_cast<uint4*>(d16 + sp.head);
-
-  if (g == 0.f) {
-    // Unscored row, masked token or zero advantage: exact zeros, logits are not read.
-    if (tid < sp.head) d16[tid] = 0;
-    if (tid < sp.tail) d16[sp.head + (sp.nvec << 3) + tid] = 0;
-    const uint4 z = make_uint4(0, 0, 0, 0);
-    for (int64_t i = tid; i < sp.nvec; i += THREADS) st_row<LD>(dvec + i, z, pol);
-    return;
-  }
-
-  // g*e^(y-lse) = sign(g) * 2^(y*log2e - lse*log2e + log2|g|): the scale rides in the exponent.
-  const float off = lg2f(fabsf(g)) - lse * kLog2e;
-  const uint32_t sgn = g < 0.f ? 0x80008000u : 0u;
-
-  auto one = [&](float x, int64_t j) -> float {  // scalar path: signed f32 result
-    float d;
-    if (CAP) {
-      const float rr = sc.r(x);
-      const float y = fmaf(-2.0f * sc.cap, rr, sc.cap);
-      d = ex2f(fmaf(y, kLog2e, off));
-      d = g < 0.f ? -d : d;
-      if (j == cl) d -= g;
-      d *= 4.0f * rr * (1.0f - rr);
-    } else {
-      d = ex2f(fmaf(x, kLog2e, off));
-      d = g < 0.f ? -d : d;
-      if (j == cl) d -= g;
-    }
-    return d;
-  };
-
-  if (tid < sp.head) {
-    const float x = __uint_as_float(uint32_t(x16[tid]) << 16);
-    d16[tid] = __bfloat16_as_ushort(__float2bfloat16_rn(one(x, tid)));
-  }
-  if (tid < sp.tail) {
-    const int64_t j = sp.head + (sp.nvec << 3) + tid;
-    const float x = __uint_as_float(uint32_t(x16[j]) << 16);
-    d16[j] = __bfloat16_as_ushort(__float2bfloat16_rn(one(x, j)));
-  }
-
-  const uint4* xvec = reinterpret_cast<const uint4*>(x16 + sp.head);
-  // Vector that holds the chosen column (or -1).
-  const int64_t cv = (cl >= sp.head && cl < sp.head + (sp.nvec << 3)) ? ((cl - sp.head) >> 3) : -1;
-
-  auto do_vec = [&](const uint4& v, int64_t idx) -> uint4 {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    uint32_t o[4];
-    if (!CAP && idx != cv) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = ex2f(fmaf(bf16lo(w[j]), kLog2e, off));
-        const float c = ex2f(fmaf(bf16hi(w[j]), kLog2e, off));
-        o[j] = pack_bf16x2(a, c) ^ sgn;
-      }
-    } else {
-      const int64_t j0 = sp.head + (idx << 3);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = one(bf16lo(w[j]), j0 + 2 * j);
-        const float c = one(bf16hi(w[j]), j0 + 2 * j + 1);
-        o[j] = pack_bf16x2(a, c);
-      }
-    }
-    return make_uint4(o[0], o[1], o[2], o[3]);
-  };
-
-  constexpr int LDX = (LD == 0) ? 1 : LD;  // never the non-coherent path: the output may alias the input
-  int64_t i = tid;
-  for (; i + int64_t(UNROLL - 1) * THREADS < sp.nvec; i += int64_t(UNROLL) * THREADS) {
-    uint4 v[UNROLL];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) v[u] = ld_row<LDX>(xvec + i + int64_t(u) * THREADS, pol);
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u)
-      st_row<LD>(dvec + i + int64_t(u) * THREADS, do_vec(v[u], i + int64_t(u) * THREADS), pol);
-  }
-  for (; i < sp.nvec; i += THREADS) {
-    const uint4 v = ld_row<LDX>(xvec + i, pol);
-    st_row<LD>(dvec + i, do_vec(v, i), pol);
   }
 }
 

@@ -131,6 +131,9 @@ class TokenLossProblem:
         self.partials: Optional[torch.Tensor] = None
         self.gathered: Optional[torch.Tensor] = None
         self.n_shards = 0
+        self.shard_rank = 0
+        self.peer_ptrs = None      # device addresses of every rank's exchange buffer (fused sharded path)
+        self.exchange_epoch = 0
 
     def args(self) -> GrpoArgs:
         a = GrpoArgs()
@@ -152,6 +155,10 @@ class TokenLossProblem:
         a.dlogits = _ptr(self.dlogits)
         a.partials, a.gathered_partials, a.n_shards = _ptr(self.partials), _ptr(self.gathered), self.n_shards
         a.device_status = _ptr(self.device_status)
+        a.shard_rank, a.exchange_epoch = self.shard_rank, self.exchange_epoch
+        if self.peer_ptrs is not None:
+            for q, ptr in enumerate(self.peer_ptrs):
+                a.peer_exchange[q] = ptr
         return a
 
     def alloc_dlogits(self, inplace: bool = False) -> torch.Tensor:

@@ -38,6 +38,42 @@ def exchange_partials(partials: torch.Tensor, group=None, out: Optional[torch.Te
     return out
 
 
+class PeerExchange:
+    """Exchange buffers of the fused sharded kernel: one zeroed device buffer per rank, mapped into
+    every other rank's address space through CUDA IPC (one process per GPU on one node, all GPUs
+    visible to every process).  The kernels only ever STORE into a peer's buffer and poll their own."""
+
+    def __init__(self, n_tokens: int, device: torch.device, group=None):
+        from . import _lib
+
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("the fused sharded kernel supports at most 8 vocabulary shards")
+        self.n_tokens = int(n_tokens)
+        nbytes = int(_lib.load().mllm_grpo_exchange_bytes(self.n_tokens, self.world))
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        torch.cuda.synchronize(device)
+        handle = self.buf.untyped_storage()._share_cuda_()
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self._peer_storages = []
+        self.ptrs = []
+        for q, h in enumerate(handles):
+            if q == self.rank:
+                self.ptrs.append(self.buf.data_ptr())
+                continue
+            st = torch.UntypedStorage._new_shared_cuda(*h)
+            self._peer_storages.append(st)
+            self.ptrs.append(st.data_ptr())
+        self.epoch = 0
+        dist.barrier(group=group)  # every buffer is zeroed and mapped before anyone stores into it
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+
 class VocabParallelLoss:
     """fwd+bwd of the loss on this rank's column shard.  Buffers are allocated once and reused."""
 
@@ -50,6 +86,7 @@ class VocabParallelLoss:
         self.cfg = cfg or LossConfig()
         self._gathered = None
         self._partials = None
+        self._peer = None
 
     def problem(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None, ref_logps=None,
                 scored_rows=None) -> TokenLossProblem:
@@ -84,3 +121,22 @@ class VocabParallelLoss:
         d = self.backward(p, dlogits)
         return {"loss": p.loss.reshape(()), "per_token_logps": p.per_token_logps, "token_entropy": p.token_entropy,
                 "dlogits": d, "problem": p}
+
+    def value_and_grad_fused(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None,
+                             ref_logps=None, dlogits=None, grad_scale: float = 1.0) -> dict:
+        """Same result as value_and_grad through ONE kernel per GPU (mllm_grpo_fwd_bwd_sharded): the
+        per-token partials cross NVLink as peer stores issued by the kernel itself, and the row shard
+        is re-read from L2 for the backward.  All ranks must call it the same number of times."""
+        p = self.problem(shard_logits, token_ids, mask, advantages, total_valid, old_logps, ref_logps)
+        if self._peer is None or self._peer.n_tokens != p.N:
+            self._peer = PeerExchange(p.N, shard_logits.device, self.group)
+        p.peer_ptrs, p.shard_rank, p.n_shards = self._peer.ptrs, self.rank, self.world
+        p.exchange_epoch = self._peer.next_epoch()
+        p.grad_scale = float(grad_scale)
+        if dlogits is not None:
+            p.dlogits = dlogits
+        else:
+            p.alloc_dlogits()
+        p.run("mllm_grpo_fwd_bwd_sharded")
+        return {"loss": p.loss.reshape(()), "per_token_logps": p.per_token_logps, "token_entropy": p.token_entropy,
+                "dlogits": p.dlogits, "problem": p}

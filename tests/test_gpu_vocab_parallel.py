@@ -1,0 +1,81 @@
+"""Vocabulary-parallel paths on real GPUs.
+
+World size 1 always runs (the fused sharded kernel then exchanges with itself, which exercises the
+publish / wait / merge protocol and both epoch parities on one GPU).  With two or more GPUs a
+two-rank job is spawned: every rank checks the NCCL path and the fused peer-store path against the
+CPU oracle, including several back-to-back calls without any barrier in between."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tests.util import ENT_ATOL, LP_ATOL, assert_dlogits_close, assert_loss_close, make_case, to_device
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run_rank(rank, world, port, ret):
+    import mllm_jax_b200 as G
+    from mllm_jax_b200.vocab_parallel import VocabParallelLoss
+    from oracle import grpo_oracle as O
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl" if world > 1 else "gloo", rank=rank, world_size=world,
+                            device_id=dev if world > 1 else None)
+    try:
+        B, L, V = 3, 41, 4096 * world
+        logits, inputs = make_case(B, L, V, seed=91, old="wide", ref=True)
+        attrs = dict(beta=0.04, epsilon_low=0.2, epsilon_high=0.3)
+        ref = O.reference_value_and_grad(logits, inputs, **attrs)
+        vp = VocabParallelLoss(V, G.LossConfig(**attrs))
+        din = to_device(inputs, dev)
+        # the shard as its own contiguous tensor, aligned ids (flat layout: score rows 0..L-2 against ids 1..L-1)
+        shard = logits[:, :-1, vp.start:vp.stop].contiguous().to(dev)
+        args = (shard, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"],
+                din["total_valid_token_count"], din["old_per_token_logps"], din["ref_per_token_logps"])
+        want_d = ref["dlogits"][:, :-1, vp.start:vp.stop]
+        outs = {"nccl": vp.value_and_grad(*args) if world > 1 else None}
+        for i in range(3):  # three fused calls in a row: both epoch parities, no barrier between them
+            outs[f"fused{i}"] = vp.value_and_grad_fused(*args, dlogits=torch.empty_like(shard))
+        torch.cuda.synchronize()
+        for name, out in outs.items():
+            if out is None:
+                continue
+            assert G.ops.check_device_status(out["problem"]) == 0, name
+            assert (out["per_token_logps"].cpu() - ref["per_token_logps"]).abs().max() <= LP_ATOL, name
+            assert (out["token_entropy"].cpu() - ref["token_entropy"]).abs().max() <= ENT_ATOL, name
+            assert_loss_close(out["loss"].item(), ref["loss"].item(), what=name)
+            assert_dlogits_close(out["dlogits"], want_d, what=name)
+        ret[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+def _spawn(world):
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_run_rank, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert dict(ret) == {r: "ok" for r in range(world)}
+
+
+@pytest.mark.timeout(300)
+def test_fused_sharded_kernel_world_size_one(cuda):
+    _spawn(1)
+
+
+@pytest.mark.timeout(300)
+def test_two_ranks_nccl_and_fused(cuda):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _spawn(2)
