@@ -171,6 +171,13 @@ int mllm_grpo_combine(const mllm_grpo_args* args, void* stream);
  * after a bounded wait and sets MLLM_GRPO_DEV_WAIT_TIMEOUT in *device_status. */
 int mllm_grpo_fwd_bwd_sharded(const mllm_grpo_args* args, void* stream);
 
+/* Lets kernels on the CURRENT device store into memory of peer_device (cudaDeviceEnablePeerAccess;
+ * "already enabled" counts as success).  Call once per peer before mllm_grpo_fwd_bwd_sharded when
+ * the exchange buffers were mapped by a route that does not enable it for the current device
+ * (CUDA IPC handles opened under the owner's device do not).  MLLM_GRPO_ERR_UNSUPPORTED if the
+ * two devices cannot reach each other. */
+int mllm_grpo_enable_peer_access(int peer_device);
+
 /* Bytes of one rank's exchange buffer for n_tokens = B*T and n_shards ranks. */
 int64_t mllm_grpo_exchange_bytes(int64_t n_tokens, int32_t n_shards);
 

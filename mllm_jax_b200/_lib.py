@@ -18,7 +18,7 @@ EXPORTS = (
     "mllm_grpo_fwd", "mllm_grpo_bwd", "mllm_grpo_fwd_bwd", "mllm_grpo_fwd_partials", "mllm_grpo_combine",
     "mllm_grpo_logprobs", "mllm_grpo_workspace_bytes", "mllm_grpo_abi_version", "mllm_grpo_status_string",
     "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count", "mllm_grpo_fwd_static_scratch",
-    "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_exchange_bytes",
+    "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_exchange_bytes", "mllm_grpo_enable_peer_access",
 )
 
 
@@ -73,6 +73,8 @@ def load():
         fn.restype = C.c_int
     lib.mllm_grpo_workspace_bytes.argtypes = [C.c_int64]
     lib.mllm_grpo_workspace_bytes.restype = C.c_int64
+    lib.mllm_grpo_enable_peer_access.argtypes = [C.c_int]
+    lib.mllm_grpo_enable_peer_access.restype = C.c_int
     lib.mllm_grpo_exchange_bytes.argtypes = [C.c_int64, C.c_int32]
     lib.mllm_grpo_exchange_bytes.restype = C.c_int64
     lib.mllm_grpo_abi_version.restype = C.c_int

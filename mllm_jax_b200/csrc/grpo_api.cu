@@ -215,6 +215,22 @@ int mllm_grpo_combine(const mllm_grpo_args* args, void* stream) {
   return MLLM_GRPO_OK;
 }
 
+int mllm_grpo_enable_peer_access(int peer_device) {
+  int dev = -1, can = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return MLLM_GRPO_ERR_NO_DEVICE;
+  if (peer_device == dev) return MLLM_GRPO_OK;
+  if (cudaDeviceCanAccessPeer(&can, dev, peer_device) != cudaSuccess || !can) {
+    (void)cudaGetLastError();
+    return MLLM_GRPO_ERR_UNSUPPORTED;
+  }
+  const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();
+    return MLLM_GRPO_OK;
+  }
+  return e == cudaSuccess ? MLLM_GRPO_OK : fail_cuda(e);
+}
+
 int64_t mllm_grpo_exchange_bytes(int64_t n_tokens, int32_t n_shards) {
   if (n_tokens <= 0 || n_shards <= 0 || n_shards > MLLM_GRPO_MAX_SHARDS) return 0;
   // two epoch parities x n_shards senders x n_tokens x (float4 partial + int32 flag)

@@ -39,34 +39,36 @@ def exchange_partials(partials: torch.Tensor, group=None, out: Optional[torch.Te
 
 
 class PeerExchange:
-    """Exchange buffers of the fused sharded kernel: one zeroed device buffer per rank, mapped into
-    every other rank's address space through CUDA IPC (one process per GPU on one node, all GPUs
-    visible to every process).  The kernels only ever STORE into a peer's buffer and poll their own."""
+    """Exchange buffers of the fused sharded kernel: one zeroed symmetric-memory buffer per rank,
+    mapped into every rank's address space by torch.distributed's symmetric memory (cuMem handles
+    with access granted to the local device).  One process per GPU on one node.  The kernels only
+    ever STORE into a peer's buffer and poll their own."""
 
     def __init__(self, n_tokens: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
         from . import _lib
 
-        self.group = group
+        self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         if self.world > 8:
             raise ValueError("the fused sharded kernel supports at most 8 vocabulary shards")
         self.n_tokens = int(n_tokens)
         nbytes = int(_lib.load().mllm_grpo_exchange_bytes(self.n_tokens, self.world))
-        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
-        torch.cuda.synchronize(device)
-        handle = self.buf.untyped_storage()._share_cuda_()
-        handles = [None] * self.world
-        dist.all_gather_object(handles, handle, group=group)
-        self._peer_storages = []
-        self.ptrs = []
-        for q, h in enumerate(handles):
-            if q == self.rank:
-                self.ptrs.append(self.buf.data_ptr())
-                continue
-            st = torch.UntypedStorage._new_shared_cuda(*h)
-            self._peer_storages.append(st)
-            self.ptrs.append(st.data_ptr())
+        if self.world == 1:
+            self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+            self.ptrs = [self.buf.data_ptr()]
+            self.handle = None
+        else:
+            self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+            self.buf.zero_()
+            torch.cuda.synchronize(device)
+            self.handle = symm_mem.rendezvous(self.buf, self.group)
+            self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            if len(self.ptrs) != self.world or self.ptrs[self.rank] != self.buf.data_ptr():
+                raise RuntimeError("symmetric memory rendezvous returned unexpected buffer pointers")
         self.epoch = 0
+        torch.cuda.synchronize(device)
         dist.barrier(group=group)  # every buffer is zeroed and mapped before anyone stores into it
 
     def next_epoch(self) -> int:
