@@ -104,10 +104,7 @@ static int validate(const mllm_grpo_args* a, unsigned need, KernelParams* k) {
   k->device_status = a->device_status;
   k->shard_rank = a->shard_rank;
   k->exchange_epoch = a->exchange_epoch;
-  for (int q = 0; q < MLLM_GRPO_MAX_SHARDS; ++q) {
-    k->peer_data[q] = nullptr;
-    k->peer_flags[q] = nullptr;
-  }
+  for (int q = 0; q < MLLM_GRPO_MAX_SHARDS; ++q) k->peer_words[q] = nullptr;
   return MLLM_GRPO_OK;
 }
 
@@ -153,27 +150,17 @@ int mllm_grpo_fwd_bwd(const mllm_grpo_args* args, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   bool taken = false;
   cudaError_t e = cudaSuccess;
-  // Implementation choice.  Default: both passes in one kernel with the second read served by L2;
-  // rows longer than ~48 KB are split over a cluster so that few rows are in flight at a time.
-  // MLLM_GRPO_FWD_BWD_MODE overrides it: "l2cluster", "l2", "cluster" (row held in distributed
-  // shared memory, TMA in and out) or "sweeps" (separate forward and backward kernels).
+  // Implementation choice.  Default ("auto"): both passes in one kernel with the second read served
+  // by L2, long rows split over a cluster (MLLM_GRPO_L2_CLUSTER / MLLM_GRPO_L2_THREADS override the
+  // plan).  MLLM_GRPO_FWD_BWD_MODE = "cluster" selects the row-resident kernel (row held in
+  // distributed shared memory, TMA in and out), "sweeps" the separate forward and backward kernels.
   const char* mode = std::getenv("MLLM_GRPO_FWD_BWD_MODE");
   const std::string m = mode ? mode : "auto";
-  const char* env_cl = std::getenv("MLLM_GRPO_L2_CLUSTER");
-  const char* env_th = std::getenv("MLLM_GRPO_L2_THREADS");
-  const char* env_ct = std::getenv("MLLM_GRPO_L2_CTAS");
   const int ent = entropy_mode(args);
-  const int64_t row_bytes = k.vocab * 2;
-  if (m == "auto" || m == "l2cluster") {
-    int cl = row_bytes >= 192 * 1024 ? 8 : (row_bytes >= 96 * 1024 ? 4 : (row_bytes >= 48 * 1024 ? 2 : 1));
-    if (env_cl) cl = std::atoi(env_cl);
-    if (cl > 1) e = launch_two_pass_cluster(k, ent, cl, env_th ? std::atoi(env_th) : 128, s, &taken);
-    if (e == cudaSuccess && !taken && m == "auto")
-      e = launch_two_pass(k, ent, env_th ? std::atoi(env_th) : 512, env_ct ? std::atoi(env_ct) : 0, s, &taken);
-  } else if (m == "l2") {
-    e = launch_two_pass(k, ent, env_th ? std::atoi(env_th) : 512, env_ct ? std::atoi(env_ct) : 0, s, &taken);
-  } else if (m == "cluster") {
+  if (m == "cluster") {
     e = launch_fused(k, ent, s, &taken);
+  } else if (m != "sweeps") {
+    e = launch_two_pass(k, ent, false, s, &taken);
   }
   if (e != cudaSuccess) return fail_cuda(e);
   if (taken) {
@@ -233,8 +220,8 @@ int mllm_grpo_enable_peer_access(int peer_device) {
 
 int64_t mllm_grpo_exchange_bytes(int64_t n_tokens, int32_t n_shards) {
   if (n_tokens <= 0 || n_shards <= 0 || n_shards > MLLM_GRPO_MAX_SHARDS) return 0;
-  // two epoch parities x n_shards senders x n_tokens x (float4 partial + int32 flag)
-  return int64_t(2) * n_shards * n_tokens * int64_t(sizeof(float4) + sizeof(int32_t));
+  // two epoch parities x n_shards senders x n_tokens x 4 words of (float value, int32 epoch)
+  return int64_t(2) * n_shards * n_tokens * 4 * int64_t(sizeof(unsigned long long));
 }
 
 int mllm_grpo_fwd_bwd_sharded(const mllm_grpo_args* args, void* stream) {
@@ -246,18 +233,14 @@ int mllm_grpo_fwd_bwd_sharded(const mllm_grpo_args* args, void* stream) {
     return MLLM_GRPO_ERR_BAD_ATTRIBUTE;
   const int ent = entropy_mode(args);
   if (ent == 2) return MLLM_GRPO_ERR_UNSUPPORTED;  // sharded entropy needs temperature 1
-  const int64_t N = k.n_seqs * k.scored_rows;
   for (int q = 0; q < args->n_shards; ++q) {
     if (args->peer_exchange[q] == nullptr) return MLLM_GRPO_ERR_NULL_POINTER;
     if (!aligned(args->peer_exchange[q], 16)) return MLLM_GRPO_ERR_ALIGNMENT;
-    k.peer_data[q] = static_cast<float4*>(args->peer_exchange[q]);
-    k.peer_flags[q] = reinterpret_cast<int*>(k.peer_data[q] + int64_t(2) * args->n_shards * N);
+    k.peer_words[q] = static_cast<unsigned long long*>(args->peer_exchange[q]);
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const char* env_th = std::getenv("MLLM_GRPO_SHARDED_THREADS");
-  const int threads = env_th ? std::atoi(env_th) : (k.vocab * 2 >= 128 * 1024 ? 512 : 256);
   bool taken = false;
-  cudaError_t e = launch_two_pass_sharded(k, ent, threads, s, &taken);
+  cudaError_t e = launch_two_pass(k, ent, true, s, &taken);
   if (e != cudaSuccess) return fail_cuda(e);
   if (!taken) return MLLM_GRPO_ERR_ALIGNMENT;  // logits and dlogits rows must share their 16-byte phase
   e = launch_loss_reduce(k, s);

@@ -48,8 +48,7 @@ struct KernelParams {
   int n_shards;
   int32_t* device_status;
   // peer exchange (mllm_grpo_fwd_bwd_sharded): rank q's buffer as seen from this device
-  float4* peer_data[8];
-  int* peer_flags[8];
+  unsigned long long* peer_words[8];  // [2 parities][n_shards senders][N tokens][4] (float, epoch) words
   int shard_rank;
   int exchange_epoch;
 };

@@ -16,12 +16,11 @@ cudaError_t launch_row_stats(const KernelParams& p, int mode, int ent, cudaStrea
 cudaError_t launch_combine(const KernelParams& p, int ent, cudaStream_t s);
 cudaError_t launch_loss_reduce(const KernelParams& p, cudaStream_t s);
 cudaError_t launch_dlogits(const KernelParams& p, cudaStream_t s);
-// One-kernel forward+backward whose second read of a row is served by L2 (grpo_stream.cu).
-cudaError_t launch_two_pass(const KernelParams& p, int ent, int threads, int ctas_per_sm, cudaStream_t s, bool* taken);
-cudaError_t launch_two_pass_cluster(const KernelParams& p, int ent, int cluster, int threads, cudaStream_t s,
-                                    bool* taken);
-// Vocabulary-sharded two-pass kernel with the peer exchange inside (grpo_sharded.cu).
-cudaError_t launch_two_pass_sharded(const KernelParams& p, int ent, int threads, cudaStream_t s, bool* taken);
+// One-kernel forward+backward whose second read of a row is served by L2 (grpo_twopass.cu); long
+// rows are split over a cluster, and with sharded == true the vocabulary shards' partials are
+// exchanged over NVLink inside the kernel.  *taken is false (nothing launched) when logits and
+// dlogits rows do not share their 16-byte phase.
+cudaError_t launch_two_pass(const KernelParams& p, int ent, bool sharded, cudaStream_t s, bool* taken);
 // Row-resident fused forward+backward (grpo_fused.cu).  *taken is false when the problem does not
 // meet its alignment / size conditions; nothing is launched then and the caller uses the two sweeps.
 cudaError_t launch_fused(const KernelParams& p, int ent, cudaStream_t s, bool* taken);

@@ -1,0 +1,267 @@
+// Forward AND backward of the GRPO token loss in one kernel: each logits row (or this rank's column
+// shard of it) is streamed twice by the same CTAs, and the second read is served by L2.
+//
+//   pass 1   128-bit loads with an L2 evict_last policy, online max / sum-exp -> (M, S, U, y_c)
+//   merge    CL > 1: the row is split over a thread-block cluster of CL CTAs (CTA r takes the r-th
+//            column slice), so that CL times fewer rows are in flight and a line is re-read after
+//            only a few tens of MB have passed through L2; slices push their partial into every
+//            peer CTA's shared memory (DSMEM) and one cluster barrier publishes them.
+//   exchange SHARDED: the row's partial of this GPU's vocabulary shard is pushed to every rank's
+//            exchange buffer as four 8-byte peer stores over NVLink, each word carrying one float
+//            and the call's epoch as its flag (an aligned 8-byte store is single-copy atomic: no
+//            fence, no separate flag); then threads 0..k-1 poll, bounded, their OWN buffer until
+//            rank q's four words show the epoch.  Nothing is ever loaded from a peer; no multicast.
+//   epilogue thread 0: ratio, clip, KL, mask -> (lse, g); outputs written once per row
+//   pass 2   dlogits = g*(softmax - onehot) in bf16, evict_first loads and stores; g == 0 rows are
+//            write-only
+// While a CTA waits for peers the other resident CTAs of the SM keep streaming.  Ranks walk the rows
+// in the same order and a CTA only waits for the row it owns, so the lowest unfinished row on every
+// GPU can always make progress; waits are bounded by wall-clock time (then a status bit is raised
+// and the CTA carries on).  Exchange buffers are double-buffered by the parity of the epoch: a rank
+// can start call e+2 only after every peer has published all of call e+1, i.e. finished call e.
+#include <cstdlib>
+
+#include "grpo_cluster.cuh"
+#include "grpo_common.cuh"
+#include "grpo_launch.h"
+#include "grpo_rowpass.cuh"
+
+namespace grpo {
+
+constexpr unsigned long long kPeerWaitLimitNs = 2000000000ull;  // 2 s
+
+// One exchanged word: value bits in the low half, the epoch in the high half.
+__device__ __forceinline__ void st_word_sys(unsigned long long* p, float v, int epoch) {
+  const unsigned long long w = (static_cast<unsigned long long>(static_cast<uint32_t>(epoch)) << 32) |
+                               static_cast<unsigned long long>(__float_as_uint(v));
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long long* p) {
+  unsigned long long w;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return w;
+}
+
+__device__ __forceinline__ float4 merge_partials(const float4* parts, int count) {
+  float M = kNegInit;
+  for (int q = 0; q < count; ++q) M = fmaxf(M, parts[q].x);
+  float S = 0.f, U = 0.f, yc = 0.f;
+  for (int q = 0; q < count; ++q) {
+    const float4 part = parts[q];
+    const float e = ex2f((part.x - M) * kLog2e);
+    S = fmaf(part.y, e, S);
+    U = fmaf(part.z, e, U);
+    yc += part.w;
+  }
+  return make_float4(M, S, U, yc);
+}
+
+template <int CL, int THREADS, int UNROLL, int ENT, bool CAP, bool SHARDED>
+__global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p, const int64_t vec_per) {
+  __shared__ float red[32];
+  __shared__ float bc[2];
+  __shared__ __align__(16) float4 slots[8];  // cluster slices' partials
+  __shared__ __align__(16) float4 parts[8];  // vocabulary shards' partials
+  const int tid = threadIdx.x;
+  const uint32_t rank = CL > 1 ? cl::cluster_rank() : 0u;
+  const int64_t r = CL > 1 ? int64_t(cl::cluster_id_x()) : int64_t(blockIdx.x);
+  const int64_t b = r / p.seq_rows;
+  const int64_t t = r - b * p.seq_rows;
+  int64_t col0 = 0, ncol = p.vocab;
+  if (CL > 1) {
+    col0 = int64_t(rank) * vec_per * 8;
+    ncol = p.vocab - col0;
+    if (ncol > vec_per * 8) ncol = vec_per * 8;
+  }
+  const uint16_t* x16 = reinterpret_cast<const uint16_t*>(p.logits + r * p.row_stride) + col0;
+  uint16_t* d16 = reinterpret_cast<uint16_t*>(p.dlogits + r * p.row_stride) + col0;
+  const SoftCap sc(CAP ? p.softcap : 1.0f);
+  const uint64_t keep = policy_evict_last(), drop = policy_evict_first();
+  if (t >= p.scored_rows) {  // every CTA of a cluster takes this branch together
+    row_pass2<THREADS, UNROLL, CAP, 2>(x16, d16, ncol, 0.f, 0.f, -1, sc, drop);
+    return;
+  }
+  // Tell the cluster peers this CTA is running (its shared memory exists) without blocking yet.
+  if (CL > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  const int64_t n = b * p.scored_rows + t;
+  const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, 2>(x16, ncol, p.inv_temperature, sc, red, keep);
+
+  int64_t c = p.chosen_ids[n];
+  if (c < 0 || c >= p.vocab_total) {
+    c = c < 0 ? 0 : p.vocab_total - 1;
+    if (tid == 0 && rank == 0 && p.device_status) atomicOr(p.device_status, MLLM_GRPO_DEV_ID_CLAMPED);
+  }
+  const int64_t cl_local = c - p.vocab_start - col0;  // chosen column relative to this CTA's columns
+  float yc_own = 0.f;
+  if (tid < 8 && cl_local >= 0 && cl_local < ncol) {
+    yc_own = __uint_as_float(uint32_t(x16[cl_local]) << 16);
+    if (CAP) yc_own = sc.y(yc_own);
+  }
+
+  if (CL > 1) {
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    if (tid < CL)
+      cl::st_cluster_f4(cl::map_to_cta(cl::smem_u32(&slots[rank]), tid), make_float4(st.M, st.S, st.U, yc_own));
+    cl::cluster_sync_all();  // release our pushes, acquire everyone else's
+  } else if (tid == 0) {
+    slots[0] = make_float4(st.M, st.S, st.U, yc_own);
+  }
+
+  if (SHARDED) {
+    const int k = p.n_shards, me = p.shard_rank;
+    const int64_t N = p.n_seqs * p.scored_rows;
+    const int64_t half = int64_t(p.exchange_epoch & 1) * int64_t(k) * N;  // parity half of every buffer
+    if (CL == 1) __syncthreads();                                          // slots[0] visible to threads < k
+    if (tid < k) {
+      if (rank == 0) {  // one CTA per row talks to the other GPUs
+        const float4 mine = merge_partials(slots, CL);
+        unsigned long long* dst = p.peer_words[tid] + (half + int64_t(me) * N + n) * 4;
+        st_word_sys(dst + 0, mine.x, p.exchange_epoch);
+        st_word_sys(dst + 1, mine.y, p.exchange_epoch);
+        st_word_sys(dst + 2, mine.z, p.exchange_epoch);
+        st_word_sys(dst + 3, mine.w, p.exchange_epoch);
+      }
+      // wait for rank `tid`'s partial of this row in OUR buffer
+      const unsigned long long* src = p.peer_words[me] + (half + int64_t(tid) * N + n) * 4;
+      const uint32_t want = static_cast<uint32_t>(p.exchange_epoch);
+      float got[4];
+      unsigned long long t0 = 0;
+      bool timed_out = false;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        unsigned long long w = ld_word_sys(src + i);
+        while (static_cast<uint32_t>(w >> 32) != want && !timed_out) {
+          if (t0 == 0) t0 = cl::globaltimer();
+          if (cl::globaltimer() - t0 > kPeerWaitLimitNs) {
+            timed_out = true;
+            if (p.device_status) atomicOr(p.device_status, MLLM_GRPO_DEV_WAIT_TIMEOUT);
+            break;
+          }
+          __nanosleep(32);
+          w = ld_word_sys(src + i);
+        }
+        got[i] = __uint_as_float(static_cast<uint32_t>(w));
+      }
+      parts[tid] = make_float4(got[0], got[1], got[2], got[3]);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const float4 m = SHARDED ? merge_partials(parts, p.n_shards) : merge_partials(slots, CL);
+    RowStats all;
+    all.M = m.x;
+    all.S = m.y;
+    all.U = m.z;
+    all.S2 = st.S2;  // temperature != 1 entropy exists only unsplit (CL == 1, not sharded)
+    all.U2 = st.U2;
+    const TokenOut o = token_epilogue<ENT>(p, n, b, all, m.w);
+    if (rank == 0) {
+      p.per_token_logps[n] = o.lp;
+      if (ENT != 0 && p.token_entropy) p.token_entropy[n] = o.entropy;
+      p.lse[n] = o.lse;
+      p.grad_coef[n] = o.grad_coef;
+      p.loss_terms[n] = o.loss_term;
+    }
+    const float nv = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
+    const float gs = p.grad_scale_dev ? *p.grad_scale_dev : p.grad_scale;
+    bc[0] = o.grad_coef * gs / nv;
+    bc[1] = o.lse;
+  }
+  __syncthreads();
+  row_pass2<THREADS, UNROLL, CAP, 2>(x16, d16, ncol, bc[0], bc[1], cl_local, sc, drop);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+template <int CL, int THREADS, int UNROLL, int ENT, bool CAP, bool SHARDED>
+cudaError_t launch_k(const KernelParams& p, cudaStream_t s) {
+  const int64_t R = p.n_seqs * p.seq_rows;
+  const int64_t nvec = p.vocab / 8;
+  const int64_t per = (nvec + CL - 1) / CL;
+  auto kern = two_pass_kernel<CL, THREADS, UNROLL, ENT, CAP, SHARDED>;
+  cudaError_t e;
+  if (CL > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3(static_cast<unsigned>(R * CL), 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kern, p, per);
+  } else {
+    kern<<<static_cast<unsigned>(R), THREADS, 0, s>>>(p, per);
+    e = cudaGetLastError();
+  }
+  count_launch();
+  return e;
+}
+
+template <int CL, int THREADS, int UNROLL, bool SHARDED>
+cudaError_t launch_e(const KernelParams& p, int ent, cudaStream_t s) {
+  const bool cap = p.softcap > 0.f;
+  if (ent == 0) return cap ? launch_k<CL, THREADS, UNROLL, 0, true, SHARDED>(p, s) : launch_k<CL, THREADS, UNROLL, 0, false, SHARDED>(p, s);
+  if (ent == 1) return cap ? launch_k<CL, THREADS, UNROLL, 1, true, SHARDED>(p, s) : launch_k<CL, THREADS, UNROLL, 1, false, SHARDED>(p, s);
+  if (CL == 1 && !SHARDED)
+    return cap ? launch_k<1, THREADS, UNROLL, 2, true, false>(p, s) : launch_k<1, THREADS, UNROLL, 2, false, false>(p, s);
+  return cudaErrorInvalidValue;
+}
+
+template <int CL, bool SHARDED>
+cudaError_t launch_t(const KernelParams& p, int ent, int threads, cudaStream_t s) {
+  if (threads <= 128) return launch_e<CL, 128, 8, SHARDED>(p, ent, s);
+  if (threads <= 256 || CL > 1) return launch_e<CL, 256, 4, SHARDED>(p, ent, s);
+  return launch_e<CL, 512, 4, SHARDED>(p, ent, s);
+}
+
+template <bool SHARDED>
+cudaError_t launch_c(const KernelParams& p, int ent, int cluster, int threads, cudaStream_t s) {
+  switch (cluster) {
+    case 1: return launch_t<1, SHARDED>(p, ent, threads, s);
+    case 2: return launch_t<2, SHARDED>(p, ent, threads, s);
+    case 4: return launch_t<4, SHARDED>(p, ent, threads, s);
+    default: return launch_t<8, SHARDED>(p, ent, threads, s);
+  }
+}
+
+}  // namespace
+
+// Cluster size and thread count for a row of `vocab` columns: slices of roughly 32-48 KB.
+void two_pass_plan(const KernelParams& p, int ent, int* cluster, int* threads) {
+  const int64_t row_bytes = p.vocab * 2;
+  int cl = row_bytes >= 192 * 1024 ? 8 : (row_bytes >= 96 * 1024 ? 4 : (row_bytes >= 56 * 1024 ? 2 : 1));
+  const bool aligned16 = !(p.vocab & 7) && !(p.row_stride & 7) && !(reinterpret_cast<uintptr_t>(p.logits) & 15) &&
+                         !(reinterpret_cast<uintptr_t>(p.dlogits) & 15);
+  const char* env_cl = std::getenv("MLLM_GRPO_L2_CLUSTER");
+  if (env_cl) cl = std::atoi(env_cl);
+  if (cl != 1 && cl != 2 && cl != 4 && cl != 8) cl = 1;
+  const int64_t nvec = p.vocab / 8;
+  if (cl > 1) {
+    const int64_t per = (nvec + cl - 1) / cl;
+    if (!aligned16 || ent == 2 || nvec - (cl - 1) * per <= 0 || p.n_seqs * p.seq_rows * cl >= (int64_t(1) << 31)) cl = 1;
+  }
+  const char* env_th = std::getenv("MLLM_GRPO_L2_THREADS");
+  int th = env_th ? std::atoi(env_th) : (cl > 1 ? 128 : (row_bytes >= 64 * 1024 ? 512 : 256));
+  *cluster = cl;
+  *threads = th;
+}
+
+// *taken is false (nothing launched) when logits and dlogits rows do not share their 16-byte phase.
+cudaError_t launch_two_pass(const KernelParams& p, int ent, bool sharded, cudaStream_t s, bool* taken) {
+  const uintptr_t ax = reinterpret_cast<uintptr_t>(p.logits), ad = reinterpret_cast<uintptr_t>(p.dlogits);
+  *taken = ((ax ^ ad) & 15) == 0;
+  if (!*taken) return cudaSuccess;
+  int cluster = 1, threads = 256;
+  two_pass_plan(p, ent, &cluster, &threads);
+  return sharded ? launch_c<true>(p, ent, cluster, threads, s) : launch_c<false>(p, ent, cluster, threads, s);
+}
+
+}  // namespace grpo

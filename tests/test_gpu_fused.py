@@ -175,9 +175,9 @@ def test_fused_equals_two_sweeps_closely(cuda):
     assert (da - db).abs().max() <= 0.01 * db.abs().max()
 
 
-@pytest.mark.parametrize("mode,cluster,threads", [("l2", 0, 512), ("l2", 0, 1024), ("l2cluster", 2, 512),
-                                                  ("l2cluster", 4, 256), ("l2cluster", 4, 128), ("l2cluster", 8, 128),
-                                                  ("cluster", 0, 0), ("sweeps", 0, 0)])
+@pytest.mark.parametrize("mode,cluster,threads", [("auto", 1, 512), ("auto", 1, 128), ("auto", 2, 256),
+                                                  ("auto", 4, 256), ("auto", 4, 128), ("auto", 8, 128),
+                                                  ("auto", 0, 0), ("cluster", 0, 0), ("sweeps", 0, 0)])
 @pytest.mark.parametrize("kind", ["kl", "softcap", "shifted_tail"])
 def test_every_fwd_bwd_mode(cuda, mode, cluster, threads, kind):
     """All implementations behind mllm_grpo_fwd_bwd give the oracle's answer."""
