@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--vocab", type=int, default=0, help="override the workload's vocabulary size (tuning only)")
+    ap.add_argument("--rows", type=int, default=0, help="override the number of sequences (tuning only)")
     ap.add_argument("--vp-mode", default="fused", choices=["fused", "nccl"],
                     help="N>1: exchange inside the kernel over peer stores, or three kernels + NCCL all-gather")
     return ap.parse_args()
@@ -167,6 +169,10 @@ def main():
     _lib.load()
 
     w = synth.CONFIGS[args.workload]
+    if args.vocab:
+        w = synth.scaled(w, vocab=args.vocab, name=w.name + f"-V{args.vocab}")
+    if args.rows:
+        w = synth.scaled(w, n_seqs=args.rows, name=w.name + f"-B{args.rows}")
     cfg = G.LossConfig(epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high, beta=w.beta, softcap=w.softcap)
     N, V = w.n_tokens, w.vocab
 
@@ -174,10 +180,14 @@ def main():
         data = synth.make_inputs(w, seed=args.seed, device=str(dev))
         dlogits = torch.empty_like(data["logits"])
 
+        first = G.grpo_value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
+                                      data["total_valid"], data["old_logps"], data["ref_logps"], cfg=cfg,
+                                      dlogits=dlogits)
+        plan1 = first["problem"]  # buffers bound once (static shapes); a step relaunches on the same addresses
+
         def step():
-            return G.grpo_value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
-                                         data["total_valid"], data["old_logps"], data["ref_logps"], cfg=cfg,
-                                         dlogits=dlogits)
+            plan1.run("mllm_grpo_fwd_bwd", reuse_args=True)
+            return first
         parallelism = "single"
     else:
         from mllm_jax_b200.vocab_parallel import VocabParallelLoss
@@ -192,11 +202,17 @@ def main():
         data["ref_logps"] = lp + (data["ref_logps"] - data["exact_logps"])
         dlogits = torch.empty_like(data["logits"])
 
-        vp_call = vp.value_and_grad_fused if args.vp_mode == "fused" else vp.value_and_grad
+        call_args = (data["logits"], data["token_ids"], data["mask"], data["advantages"], data["total_valid"],
+                     data["old_logps"], data["ref_logps"])
+        if args.vp_mode == "fused":
+            # buffers bound once (static shapes), every step relaunches on the same addresses
+            plan = vp.plan_fused(*call_args, dlogits=dlogits)
 
-        def step():
-            return vp_call(data["logits"], data["token_ids"], data["mask"], data["advantages"],
-                           data["total_valid"], data["old_logps"], data["ref_logps"], dlogits=dlogits)
+            def step():
+                return vp.step_fused(plan)
+        else:
+            def step():
+                return vp.value_and_grad(*call_args, dlogits=dlogits)
         parallelism = f"vocab-parallel tp{world}, exchange: " + (
             "peer stores inside the kernel" if args.vp_mode == "fused" else "NCCL all-gather between kernels")
 

@@ -87,27 +87,6 @@ __device__ __forceinline__ void st_row(uint4* p, const uint4& v, uint64_t pol) {
     stg_stream(p, v);
 }
 
-template <int THREADS>
-__device__ __forceinline__ float block_max(float v, float* red) {
-  v = warp_max(v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  __syncthreads();  // protect `red` from the previous use
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float r = (lane < THREADS / 32) ? red[lane] : kNegInit;
-  return warp_max(r);
-}
-template <int THREADS>
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  __syncthreads();
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float r = (lane < THREADS / 32) ? red[lane] : 0.f;
-  return warp_sum(r);
-}
-
 // Fold a batch of NV vectors into the accumulator.
 template <int ENT, bool CAP, int NV>
 __device__ __forceinline__ void fold_vectors(RowAcc<ENT>& acc, const uint4 (&v)[NV], float inv_temp,
@@ -179,20 +158,46 @@ __device__ __forceinline__ RowStats row_pass1(const uint16_t* row16, int64_t V, 
     v[0] = ld_row<LD>(vec + i, pol);
     fold_vectors<ENT, CAP, 1>(acc, v, inv_temp, k2, sc);
   }
-  // Block reduction: common max first, then sums rescaled to it.
+  // Block reduction with ONE barrier: warps merge (m, s, u) by shuffles, lane 0 parks the warp's
+  // result in shared memory, and after the barrier every warp merges the per-warp entries again by
+  // shuffles.  `red` must hold 5 floats per warp (160 floats).
+  constexpr int NW = THREADS / 32;
+  const int lane = tid & 31, warp = tid >> 5;
+  const float Mw = warp_max(acc.m);
+  const float dw = (acc.m - Mw) * kLog2e;
+  const float sw = ex2f(dw);
+  const float Sw = warp_sum(acc.s * sw);
+  float Uw = 0.f, S2w = 0.f, U2w = 0.f;
+  if (ENT == 1) Uw = warp_sum(acc.u * sw);
+  if (ENT == 2) {
+    const float sw2 = ex2f(dw * inv_temp);
+    S2w = warp_sum(acc.s2 * sw2);
+    U2w = warp_sum(acc.u2 * sw2);
+  }
+  if (lane == 0) {
+    red[warp] = Mw;
+    red[32 + warp] = Sw;
+    if (ENT == 1) red[64 + warp] = Uw;
+    if (ENT == 2) {
+      red[96 + warp] = S2w;
+      red[128 + warp] = U2w;
+    }
+  }
+  __syncthreads();
+  const float m_in = lane < NW ? red[lane] : kNegInit;
   RowStats st;
-  st.M = block_max<THREADS>(acc.m, red);
-  const float d = (acc.m - st.M) * kLog2e;
-  const float scl = ex2f(d);
-  st.S = block_sum<THREADS>(acc.s * scl, red);
+  st.M = warp_max(m_in);
+  const float db = (m_in - st.M) * kLog2e;
+  const float sb = ex2f(db);
+  st.S = warp_sum(lane < NW ? red[32 + lane] * sb : 0.f);
   st.U = 0.f;
   st.S2 = 0.f;
   st.U2 = 0.f;
-  if (ENT == 1) st.U = block_sum<THREADS>(acc.u * scl, red);
+  if (ENT == 1) st.U = warp_sum(lane < NW ? red[64 + lane] * sb : 0.f);
   if (ENT == 2) {
-    const float scl2 = ex2f(d * inv_temp);
-    st.S2 = block_sum<THREADS>(acc.s2 * scl2, red);
-    st.U2 = block_sum<THREADS>(acc.u2 * scl2, red);
+    const float sb2 = ex2f(db * inv_temp);
+    st.S2 = warp_sum(lane < NW ? red[96 + lane] * sb2 : 0.f);
+    st.U2 = warp_sum(lane < NW ? red[128 + lane] * sb2 : 0.f);
   }
   return st;
 }

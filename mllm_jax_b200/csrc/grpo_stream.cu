@@ -21,7 +21,7 @@ namespace grpo {
 // MODE: 0 full forward (epilogue + residuals + loss terms), 1 shard partials, 2 log-probs only.
 template <int THREADS, int UNROLL, int ENT, bool CAP, int MODE>
 __global__ void __launch_bounds__(THREADS) row_stats_kernel(const KernelParams p) {
-  __shared__ float red[32];
+  __shared__ float red[160];
   const int tid = threadIdx.x;
   const int64_t n = blockIdx.x;  // scored token index
   const int64_t b = n / p.scored_rows;

@@ -58,7 +58,7 @@ __device__ __forceinline__ float4 merge_partials(const float4* parts, int count)
 
 template <int CL, int THREADS, int UNROLL, int ENT, bool CAP, bool SHARDED>
 __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p, const int64_t vec_per) {
-  __shared__ float red[32];
+  __shared__ float red[160];
   __shared__ float bc[2];
   __shared__ __align__(16) float4 slots[8];  // cluster slices' partials
   __shared__ __align__(16) float4 parts[8];  // vocabulary shards' partials
@@ -84,8 +84,7 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
   // Tell the cluster peers this CTA is running (its shared memory exists) without blocking yet.
   if (CL > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
   const int64_t n = b * p.scored_rows + t;
-  const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, 2>(x16, ncol, p.inv_temperature, sc, red, keep);
-
+  // Everything the epilogue needs is requested before the first pass, so its latency is hidden.
   int64_t c = p.chosen_ids[n];
   if (c < 0 || c >= p.vocab_total) {
     c = c < 0 ? 0 : p.vocab_total - 1;
@@ -93,10 +92,17 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
   }
   const int64_t cl_local = c - p.vocab_start - col0;  // chosen column relative to this CTA's columns
   float yc_own = 0.f;
-  if (tid < 8 && cl_local >= 0 && cl_local < ncol) {
-    yc_own = __uint_as_float(uint32_t(x16[cl_local]) << 16);
-    if (CAP) yc_own = sc.y(yc_own);
+  if (tid < 8 && cl_local >= 0 && cl_local < ncol) yc_own = __uint_as_float(uint32_t(x16[cl_local]) << 16);
+  TokenSide side = {};
+  float nv_pre = 1.f, gs_pre = 1.f;
+  if (tid == 0) {
+    side = load_token_side(p, n, b);
+    nv_pre = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
+    gs_pre = p.grad_scale_dev ? *p.grad_scale_dev : p.grad_scale;
   }
+
+  const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, 2>(x16, ncol, p.inv_temperature, sc, red, keep);
+  if (CAP && tid < 8 && cl_local >= 0 && cl_local < ncol) yc_own = sc.y(yc_own);
 
   if (CL > 1) {
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
@@ -154,7 +160,7 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
     all.U = m.z;
     all.S2 = st.S2;  // temperature != 1 entropy exists only unsplit (CL == 1, not sharded)
     all.U2 = st.U2;
-    const TokenOut o = token_epilogue<ENT>(p, n, b, all, m.w);
+    const TokenOut o = token_epilogue_core<ENT>(p, all, m.w, side);
     if (rank == 0) {
       p.per_token_logps[n] = o.lp;
       if (ENT != 0 && p.token_entropy) p.token_entropy[n] = o.entropy;
@@ -162,9 +168,7 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
       p.grad_coef[n] = o.grad_coef;
       p.loss_terms[n] = o.loss_term;
     }
-    const float nv = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
-    const float gs = p.grad_scale_dev ? *p.grad_scale_dev : p.grad_scale;
-    bc[0] = o.grad_coef * gs / nv;
+    bc[0] = o.grad_coef * gs_pre / nv_pre;
     bc[1] = o.lse;
   }
   __syncthreads();
@@ -217,6 +221,7 @@ cudaError_t launch_e(const KernelParams& p, int ent, cudaStream_t s) {
 
 template <int CL, bool SHARDED>
 cudaError_t launch_t(const KernelParams& p, int ent, int threads, cudaStream_t s) {
+  if (threads <= 64 && CL == 1) return launch_e<1, 64, 8, SHARDED>(p, ent, s);
   if (threads <= 128) return launch_e<CL, 128, 8, SHARDED>(p, ent, s);
   if (threads <= 256 || CL > 1) return launch_e<CL, 256, 4, SHARDED>(p, ent, s);
   return launch_e<CL, 512, 4, SHARDED>(p, ent, s);
@@ -235,9 +240,12 @@ cudaError_t launch_c(const KernelParams& p, int ent, int cluster, int threads, c
 }  // namespace
 
 // Cluster size and thread count for a row of `vocab` columns: slices of roughly 32-48 KB.
-void two_pass_plan(const KernelParams& p, int ent, int* cluster, int* threads) {
+void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, int* threads) {
   const int64_t row_bytes = p.vocab * 2;
   int cl = row_bytes >= 192 * 1024 ? 8 : (row_bytes >= 96 * 1024 ? 4 : (row_bytes >= 56 * 1024 ? 2 : 1));
+  // With the NVLink exchange in the kernel the split did not pay on 2 GPUs (152 KB row shards:
+  // 1.99 ms unsplit, 2.01 ms CL=2, 2.06 ms CL=4): keep whole row shards per CTA.
+  if (sharded) cl = 1;
   const bool aligned16 = !(p.vocab & 7) && !(p.row_stride & 7) && !(reinterpret_cast<uintptr_t>(p.logits) & 15) &&
                          !(reinterpret_cast<uintptr_t>(p.dlogits) & 15);
   const char* env_cl = std::getenv("MLLM_GRPO_L2_CLUSTER");
@@ -249,7 +257,8 @@ void two_pass_plan(const KernelParams& p, int ent, int* cluster, int* threads) {
     if (!aligned16 || ent == 2 || nvec - (cl - 1) * per <= 0 || p.n_seqs * p.seq_rows * cl >= (int64_t(1) << 31)) cl = 1;
   }
   const char* env_th = std::getenv("MLLM_GRPO_L2_THREADS");
-  int th = env_th ? std::atoi(env_th) : (cl > 1 ? 128 : (row_bytes >= 64 * 1024 ? 512 : 256));
+  // measured on one B200 (unsplit rows): 38 KB rows 64 threads, 76 KB 256, 152 KB and longer 512
+  int th = env_th ? std::atoi(env_th) : (cl > 1 ? 128 : (row_bytes < 56 * 1024 ? 64 : (row_bytes < 112 * 1024 ? 256 : 512)));
   *cluster = cl;
   *threads = th;
 }
@@ -260,7 +269,7 @@ cudaError_t launch_two_pass(const KernelParams& p, int ent, bool sharded, cudaSt
   *taken = ((ax ^ ad) & 15) == 0;
   if (!*taken) return cudaSuccess;
   int cluster = 1, threads = 256;
-  two_pass_plan(p, ent, &cluster, &threads);
+  two_pass_plan(p, ent, sharded, &cluster, &threads);
   return sharded ? launch_c<true>(p, ent, cluster, threads, s) : launch_c<false>(p, ent, cluster, threads, s);
 }
 

@@ -165,9 +165,16 @@ class TokenLossProblem:
         self.dlogits = self.logits if inplace else torch.empty_like(self.logits)
         return self.dlogits
 
-    def run(self, entry: str) -> None:
+    def run(self, entry: str, reuse_args: bool = False) -> None:
+        """Launch one entry point on the current stream.  reuse_args=True reuses the argument struct of
+        the previous launch (same buffers and attributes; only exchange_epoch is refreshed)."""
+        if reuse_args and getattr(self, "_args", None) is not None:
+            a = self._args
+            a.exchange_epoch = self.exchange_epoch
+        else:
+            a = self._args = self.args()
         with torch.cuda.device(self.logits.device):
-            _lib.call(entry, self.args(), _stream())
+            _lib.call(entry, a, _stream())
 
 
 class _GrpoLoss(torch.autograd.Function):

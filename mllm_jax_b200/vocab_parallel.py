@@ -124,21 +124,32 @@ class VocabParallelLoss:
         return {"loss": p.loss.reshape(()), "per_token_logps": p.per_token_logps, "token_entropy": p.token_entropy,
                 "dlogits": d, "problem": p}
 
-    def value_and_grad_fused(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None,
-                             ref_logps=None, dlogits=None, grad_scale: float = 1.0) -> dict:
-        """Same result as value_and_grad through ONE kernel per GPU (mllm_grpo_fwd_bwd_sharded): the
-        per-token partials cross NVLink as peer stores issued by the kernel itself, and the row shard
-        is re-read from L2 for the backward.  All ranks must call it the same number of times."""
+    def plan_fused(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None, ref_logps=None,
+                   dlogits=None, grad_scale: float = 1.0) -> TokenLossProblem:
+        """Bind buffers once for repeated fused steps on the same addresses (static shapes, new
+        contents each step): `step_fused(plan)` then only bumps the epoch and launches."""
         p = self.problem(shard_logits, token_ids, mask, advantages, total_valid, old_logps, ref_logps)
         if self._peer is None or self._peer.n_tokens != p.N:
             self._peer = PeerExchange(p.N, shard_logits.device, self.group)
         p.peer_ptrs, p.shard_rank, p.n_shards = self._peer.ptrs, self.rank, self.world
-        p.exchange_epoch = self._peer.next_epoch()
         p.grad_scale = float(grad_scale)
         if dlogits is not None:
             p.dlogits = dlogits
         else:
             p.alloc_dlogits()
-        p.run("mllm_grpo_fwd_bwd_sharded")
+        return p
+
+    def step_fused(self, p: TokenLossProblem) -> dict:
+        p.exchange_epoch = self._peer.next_epoch()
+        p.run("mllm_grpo_fwd_bwd_sharded", reuse_args=p.exchange_epoch > 1 and getattr(p, "_planned", False))
+        p._planned = True
         return {"loss": p.loss.reshape(()), "per_token_logps": p.per_token_logps, "token_entropy": p.token_entropy,
                 "dlogits": p.dlogits, "problem": p}
+
+    def value_and_grad_fused(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None,
+                             ref_logps=None, dlogits=None, grad_scale: float = 1.0) -> dict:
+        """Same result as value_and_grad through ONE kernel per GPU (mllm_grpo_fwd_bwd_sharded): the
+        per-token partials cross NVLink as peer stores issued by the kernel itself, and the row shard
+        is re-read from L2 for the backward.  All ranks must call it the same number of times."""
+        return self.step_fused(self.plan_fused(shard_logits, token_ids, mask, advantages, total_valid, old_logps,
+                                               ref_logps, dlogits, grad_scale))

@@ -79,3 +79,33 @@ def test_two_ranks_nccl_and_fused(cuda):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _spawn(2)
+
+
+@pytest.mark.timeout(120)
+def test_missing_peer_times_out_with_status(cuda):
+    """Failure detection without a GPU fault: rank 0 of a pretended 2-rank job runs alone, so the
+    words of rank 1 never arrive.  Every wait gives up after its wall-clock limit, the kernel ends
+    normally, the context stays usable and MLLM_GRPO_DEV_WAIT_TIMEOUT is raised for the host."""
+    import mllm_jax_b200 as G
+    from mllm_jax_b200 import _lib
+
+    B, L, V = 1, 4, 512
+    logits, inputs = make_case(B, L, V, seed=92, old="none", mask_kind="ones")
+    din = to_device(inputs, cuda)
+    x = logits[:, :-1].contiguous().to(cuda)
+    p = G.TokenLossProblem(x, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"], 3.0, None, None,
+                           G.LossConfig(), scored_rows=L - 1, vocab=V, vocab_start=0, vocab_total=2 * V)
+    nbytes = int(_lib.load().mllm_grpo_exchange_bytes(p.N, 2))
+    mine = torch.zeros(nbytes, dtype=torch.uint8, device=cuda)
+    absent_peer = torch.zeros(nbytes, dtype=torch.uint8, device=cuda)  # stands in for rank 1's buffer
+    p.peer_ptrs, p.shard_rank, p.n_shards, p.exchange_epoch = [mine.data_ptr(), absent_peer.data_ptr()], 0, 2, 1
+    p.alloc_dlogits()
+    p.run("mllm_grpo_fwd_bwd_sharded")
+    torch.cuda.synchronize()
+    assert G.ops.check_device_status(p) & _lib.DEV_WAIT_TIMEOUT
+    # the context is still healthy: an ordinary call works afterwards
+    q = G.TokenLossProblem(x, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"], 3.0, None, None,
+                           G.LossConfig(), scored_rows=L - 1)
+    q.run("mllm_grpo_fwd")
+    torch.cuda.synchronize()
+    assert torch.isfinite(q.loss).all() and G.ops.check_device_status(q) == 0
