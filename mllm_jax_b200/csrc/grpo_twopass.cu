@@ -258,7 +258,7 @@ void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, i
   }
   const char* env_th = std::getenv("MLLM_GRPO_L2_THREADS");
   // measured on one B200 (unsplit rows): 38 KB rows 64 threads, 76 KB 256, 152 KB and longer 512
-  int th = env_th ? std::atoi(env_th) : (cl > 1 ? 128 : (row_bytes < 56 * 1024 ? 64 : (row_bytes < 112 * 1024 ? 256 : 512)));
+  int th = env_th ? std::atoi(env_th) : (cl > 1 ? 128 : (row_bytes < 56 * 1024 ? 64 : (row_bytes < 112 * 1024 || sharded ? 256 : 512)));
   *cluster = cl;
   *threads = th;
 }

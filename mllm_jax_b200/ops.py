@@ -66,7 +66,7 @@ class TokenLossProblem:
         if logits.dim() != 3:
             raise ValueError(f"logits must be [B, L, V], got shape {tuple(logits.shape)}")
         B, L, Vfull = logits.shape
-        if logits.stride(2) != 1 or logits.stride(0) != L * logits.stride(1):
+        if logits.stride(2) != 1 or (B > 1 and logits.stride(0) != L * logits.stride(1)):
             raise ValueError("logits must have unit stride on the vocabulary and rows evenly spaced")
         self.cfg = cfg
         self.logits = logits

@@ -45,6 +45,10 @@ class PeerExchange:
     ever STORE into a peer's buffer and poll their own."""
 
     def __init__(self, n_tokens: int, device: torch.device, group=None):
+        import os
+
+        # The kernels use plain peer stores only; keep the buffers off NVLink multicast objects.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import _lib
