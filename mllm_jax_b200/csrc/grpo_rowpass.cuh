@@ -147,7 +147,8 @@ __device__ __forceinline__ RowStats row_pass1(const uint16_t* row16, int64_t V, 
   }
   const uint4* vec = reinterpret_cast<const uint4*>(row16 + sp.head);
   int64_t i = tid;
-  for (; i + int64_t(UNROLL - 1) * THREADS < sp.nvec; i += int64_t(UNROLL) * THREADS) {
+  constexpr int64_t kStep = int64_t(UNROLL) * THREADS;
+  for (; i + kStep - THREADS < sp.nvec; i += kStep) {
     uint4 v[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) v[u] = ld_row<LD>(vec + i + int64_t(u) * THREADS, pol);
@@ -299,7 +300,8 @@ __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, in
 
   constexpr int LDX = (LD == 0) ? 1 : LD;  // never the non-coherent path: the output may alias the input
   int64_t i = tid;
-  for (; i + int64_t(UNROLL - 1) * THREADS < sp.nvec; i += int64_t(UNROLL) * THREADS) {
+  constexpr int64_t kStep = int64_t(UNROLL) * THREADS;
+  for (; i + kStep - THREADS < sp.nvec; i += kStep) {
     uint4 v[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) v[u] = ld_row<LDX>(xvec + i + int64_t(u) * THREADS, pol);

@@ -42,6 +42,10 @@ __device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long lo
   return w;
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 __device__ __forceinline__ float4 merge_partials(const float4* parts, int count) {
   float M = kNegInit;
   for (int q = 0; q < count; ++q) M = fmaxf(M, parts[q].x);
@@ -93,12 +97,11 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
   const int64_t cl_local = c - p.vocab_start - col0;  // chosen column relative to this CTA's columns
   float yc_own = 0.f;
   if (tid < 8 && cl_local >= 0 && cl_local < ncol) yc_own = __uint_as_float(uint32_t(x16[cl_local]) << 16);
-  TokenSide side = {};
-  float nv_pre = 1.f, gs_pre = 1.f;
-  if (tid == 0) {
-    side = load_token_side(p, n, b);
-    nv_pre = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
-    gs_pre = p.grad_scale_dev ? *p.grad_scale_dev : p.grad_scale;
+  if (tid == 0) {  // pull the epilogue's side inputs towards L2 without holding registers for them
+    if (p.mask) prefetch_l2(p.mask + n);
+    prefetch_l2(p.advantages + (p.adv_per_token ? n : b));
+    if (p.old_logps) prefetch_l2(p.old_logps + n);
+    if (p.ref_logps) prefetch_l2(p.ref_logps + n);
   }
 
   const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, 2>(x16, ncol, p.inv_temperature, sc, red, keep);
@@ -160,7 +163,7 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
     all.U = m.z;
     all.S2 = st.S2;  // temperature != 1 entropy exists only unsplit (CL == 1, not sharded)
     all.U2 = st.U2;
-    const TokenOut o = token_epilogue_core<ENT>(p, all, m.w, side);
+    const TokenOut o = token_epilogue<ENT>(p, n, b, all, m.w);
     if (rank == 0) {
       p.per_token_logps[n] = o.lp;
       if (ENT != 0 && p.token_entropy) p.token_entropy[n] = o.entropy;
@@ -168,7 +171,9 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
       p.grad_coef[n] = o.grad_coef;
       p.loss_terms[n] = o.loss_term;
     }
-    bc[0] = o.grad_coef * gs_pre / nv_pre;
+    const float nv = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
+    const float gs = p.grad_scale_dev ? *p.grad_scale_dev : p.grad_scale;
+    bc[0] = o.grad_coef * gs / nv;
     bc[1] = o.lse;
   }
   __syncthreads();
