@@ -121,9 +121,17 @@ typedef struct mllm_grpo_args {
                                                 entry shard_rank is this rank's own buffer */
   int32_t exchange_epoch; /* > 0, the same on every rank, +1 on every call that uses the buffers */
   int32_t reserved1;
+
+  /* ---- per-sample monitors of mllm_grpo_entropy_stats ---- */
+  float* sample_entropy;        /* [B] sum_t H_t m_t / sum_t m_t                      (train_modules :141-143) */
+  float* sample_entropy_window; /* [B] the same over valid tokens number 4..100 of a sample (:148-157) */
 } mllm_grpo_args;
 
 #define MLLM_GRPO_FLAG_SKIP_ENTROPY 1 /* do not compute token_entropy (saves one FMA per element) */
+#define MLLM_GRPO_FLAG_CE_LOSS 2      /* masked cross-entropy instead of the clipped surrogate: per-token loss
+                                         -lp, loss = sum(mask * -lp) / total_valid, dlogits =
+                                         mask/total_valid * (softmax - onehot); advantages, old_logps and
+                                         ref_logps are ignored (plugins/sft/jax/sft_module.py:29-41) */
 
 /* Forward over full rows (vocab_start = 0, vocab = vocab_total).
  * Replaces train_modules/__init__.py:118-180 (ppo/module.py:66-102 with adv_per_token = 1).
@@ -203,6 +211,13 @@ int mllm_grpo_logprobs(const mllm_grpo_args* args, void* stream);
  *     that overlap on the GPU (different streams, no ordering between them) race on it. */
 #define MLLM_GRPO_STATIC_SCRATCH_TOKENS (1 << 20)
 int mllm_grpo_fwd_static_scratch(const mllm_grpo_args* args, void* stream);
+
+/* Per-sample entropy monitors of the reference's return dict ('entropy', 'entropy_loss',
+ * train_modules/__init__.py:141-157) from token_entropy [B*T] and mask [B*T]: one CTA per sample,
+ * a block scan gives each token its running count of valid tokens.  A sample without valid tokens
+ * yields 0/0 = NaN, as in the reference.  Reads n_seqs, scored_rows, token_entropy, mask; writes
+ * sample_entropy and sample_entropy_window. */
+int mllm_grpo_entropy_stats(const mllm_grpo_args* args, void* stream);
 
 /* Bytes of loss_terms scratch a problem of n_tokens = B*T needs. */
 int64_t mllm_grpo_workspace_bytes(int64_t n_tokens);

@@ -10,12 +10,13 @@ from .ops import (  # noqa: F401
     grpo_token_loss,
     grpo_token_loss_flat,
     grpo_value_and_grad,
+    sft_cross_entropy,
     token_logprobs,
 )
 from .train_module import TrainGRPOModule, per_sample_entropy, ppo_policy_terms  # noqa: F401
 
 __all__ = [
     "GrpoError", "LIB_PATH", "LossConfig", "TokenLossProblem", "TrainGRPOModule", "grpo_token_loss",
-    "grpo_token_loss_flat", "grpo_value_and_grad", "launch_count", "per_sample_entropy", "ppo_policy_terms",
+    "grpo_token_loss_flat", "grpo_value_and_grad", "launch_count", "per_sample_entropy", "ppo_policy_terms", "sft_cross_entropy",
     "token_logprobs",
 ]

@@ -11,6 +11,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmllm_grpo.so"
 
 FLAG_SKIP_ENTROPY = 1
+FLAG_CE_LOSS = 2
 DEV_ID_CLAMPED = 1
 DEV_WAIT_TIMEOUT = 2
 
@@ -19,6 +20,7 @@ EXPORTS = (
     "mllm_grpo_logprobs", "mllm_grpo_workspace_bytes", "mllm_grpo_abi_version", "mllm_grpo_status_string",
     "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count", "mllm_grpo_fwd_static_scratch",
     "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_exchange_bytes", "mllm_grpo_enable_peer_access",
+    "mllm_grpo_entropy_stats",
 )
 
 
@@ -42,6 +44,7 @@ class GrpoArgs(C.Structure):
         ("shard_rank", C.c_int32),
         ("device_status", C.c_void_p),
         ("peer_exchange", C.c_void_p * 8), ("exchange_epoch", C.c_int32), ("reserved1", C.c_int32),
+        ("sample_entropy", C.c_void_p), ("sample_entropy_window", C.c_void_p),
     ]
 
 
@@ -67,7 +70,7 @@ def load():
     lib = C.CDLL(str(LIB_PATH))
     for name in ("mllm_grpo_fwd", "mllm_grpo_bwd", "mllm_grpo_fwd_bwd", "mllm_grpo_fwd_partials",
                  "mllm_grpo_combine", "mllm_grpo_logprobs", "mllm_grpo_fwd_static_scratch",
-                 "mllm_grpo_fwd_bwd_sharded"):
+                 "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_entropy_stats"):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(GrpoArgs), C.c_void_p]
         fn.restype = C.c_int

@@ -49,7 +49,7 @@ static int validate(const mllm_grpo_args* a, unsigned need, KernelParams* k) {
 
   if ((need & kLogits) && !a->logits) return MLLM_GRPO_ERR_NULL_POINTER;
   if ((need & kIds) && !a->chosen_ids) return MLLM_GRPO_ERR_NULL_POINTER;
-  if ((need & kEpilogueIn) && !a->advantages) return MLLM_GRPO_ERR_NULL_POINTER;
+  if ((need & kEpilogueIn) && !a->advantages && !(a->flags & MLLM_GRPO_FLAG_CE_LOSS)) return MLLM_GRPO_ERR_NULL_POINTER;
   if ((need & kEpilogueOut) && (!a->per_token_logps || !a->lse || !a->grad_coef || !a->loss || !a->loss_terms))
     return MLLM_GRPO_ERR_NULL_POINTER;
   if ((need & kEpilogueOut) && !a->total_valid_dev && !(a->total_valid == a->total_valid))
@@ -83,6 +83,7 @@ static int validate(const mllm_grpo_args* a, unsigned need, KernelParams* k) {
   k->grad_scale = a->grad_scale;
   k->total_valid = a->total_valid;
   k->adv_per_token = a->adv_per_token;
+  k->ce_loss = (a->flags & MLLM_GRPO_FLAG_CE_LOSS) ? 1 : 0;
   k->logits = static_cast<const __nv_bfloat16*>(a->logits);
   k->chosen_ids = a->chosen_ids;
   k->mask = a->mask;
@@ -200,6 +201,18 @@ int mllm_grpo_combine(const mllm_grpo_args* args, void* stream) {
   e = launch_loss_reduce(k, s);
   if (e != cudaSuccess) return fail_cuda(e);
   return MLLM_GRPO_OK;
+}
+
+int mllm_grpo_entropy_stats(const mllm_grpo_args* args, void* stream) {
+  if (args == nullptr) return MLLM_GRPO_ERR_NULL_POINTER;
+  if (args->struct_size != sizeof(mllm_grpo_args)) return MLLM_GRPO_ERR_STRUCT_SIZE;
+  if (args->n_seqs <= 0 || args->scored_rows <= 0 || args->n_seqs >= (int64_t(1) << 31)) return MLLM_GRPO_ERR_BAD_SHAPE;
+  if (!args->token_entropy || !args->mask || !args->sample_entropy || !args->sample_entropy_window)
+    return MLLM_GRPO_ERR_NULL_POINTER;
+  const cudaError_t e = launch_entropy_stats(args->token_entropy, args->mask, args->n_seqs, args->scored_rows,
+                                             args->sample_entropy, args->sample_entropy_window,
+                                             static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MLLM_GRPO_OK : fail_cuda(e);
 }
 
 int mllm_grpo_enable_peer_access(int peer_device) {

@@ -26,6 +26,7 @@ struct KernelParams {
   float inv_temperature, clip_lo, clip_hi, beta, softcap;
   float grad_scale, total_valid;
   int adv_per_token;
+  int ce_loss;  // 1: per-token loss is -lp (masked cross-entropy) instead of the clipped surrogate
   // inputs
   const __nv_bfloat16* logits;
   const int32_t* chosen_ids;
@@ -183,6 +184,12 @@ __device__ __forceinline__ TokenOut token_epilogue_core(const KernelParams& p, c
     o.entropy = 0.f;
   }
   const float m = sd.mask, A = sd.adv;
+  if (p.ce_loss) {
+    // masked cross-entropy (plugins/sft/jax/sft_module.py:36-41): loss_t = -lp_t, d loss_t / d lp_t = -1
+    o.loss_term = -m * o.lp;
+    o.grad_coef = m * p.inv_temperature;
+    return o;
+  }
   const float old = sd.has_old ? sd.old : o.lp;
   const float ratio = expf(o.lp - old);
   const float clipped = fminf(fmaxf(ratio, p.clip_lo), p.clip_hi);

@@ -21,6 +21,9 @@ cudaError_t launch_dlogits(const KernelParams& p, cudaStream_t s);
 // exchanged over NVLink inside the kernel.  *taken is false (nothing launched) when logits and
 // dlogits rows do not share their 16-byte phase.
 cudaError_t launch_two_pass(const KernelParams& p, int ent, bool sharded, cudaStream_t s, bool* taken);
+// Per-sample entropy monitors (grpo_monitors.cu).
+cudaError_t launch_entropy_stats(const float* H, const float* mask, int64_t B, int64_t T, float* ent, float* ent_win,
+                                 cudaStream_t s);
 // Row-resident fused forward+backward (grpo_fused.cu).  *taken is false when the problem does not
 // meet its alignment / size conditions; nothing is launched then and the caller uses the two sweeps.
 cudaError_t launch_fused(const KernelParams& p, int ent, cudaStream_t s, bool* taken);

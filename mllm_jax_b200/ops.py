@@ -45,6 +45,7 @@ class LossConfig:
     beta: float = 0.0
     softcap: Optional[float] = None
     compute_entropy: bool = True
+    cross_entropy: bool = False  # masked cross-entropy (SFT) instead of the clipped surrogate
 
 
 class TokenLossProblem:
@@ -144,7 +145,7 @@ class TokenLossProblem:
         a.temperature, a.epsilon_low, a.epsilon_high, a.beta = c.temperature, c.epsilon_low, c.epsilon_high, c.beta
         a.softcap = float(c.softcap) if c.softcap else 0.0
         a.adv_per_token = self.adv_per_token
-        a.flags = 0 if c.compute_entropy else _lib.FLAG_SKIP_ENTROPY
+        a.flags = (0 if c.compute_entropy else _lib.FLAG_SKIP_ENTROPY) | (_lib.FLAG_CE_LOSS if c.cross_entropy else 0)
         a.grad_scale, a.total_valid = self.grad_scale, self.total_valid
         a.logits = _ptr(self.logits)
         a.chosen_ids, a.mask, a.advantages = _ptr(self.chosen_ids), _ptr(self.mask), _ptr(self.advantages)
@@ -300,3 +301,23 @@ def token_logprobs(logits: torch.Tensor, token_ids: torch.Tensor, *, shifted: bo
 def check_device_status(prob: TokenLossProblem) -> int:
     """Synchronises and returns the MLLM_GRPO_DEV_* bits the kernels raised (0 = clean)."""
     return int(prob.device_status.item())
+
+
+def sft_cross_entropy(logits: torch.Tensor, input_ids: torch.Tensor, labels: torch.Tensor,
+                      attention_mask: Optional[torch.Tensor] = None, *, label_ignore_id: int = -100,
+                      inplace_backward: bool = False) -> dict:
+    """Causal-LM cross-entropy of TrainSftModule (plugins/sft/jax/sft_module.py:29-45) on the same
+    streaming kernels: logits [B, L, V] bf16, labels [B, L] with `label_ignore_id` on unsupervised
+    positions.  valid = (labels[:, 1:] != ignore) & attention_mask[:, 1:]; loss = sum(-lp * valid) /
+    max(valid.sum(), 1).  Returns {"loss" (differentiable w.r.t. logits), "token_count"}."""
+    shift_labels = labels[:, 1:]
+    valid = shift_labels != int(label_ignore_id)
+    if attention_mask is not None:
+        valid = valid & attention_mask[:, 1:].bool()
+    safe = torch.where(valid, shift_labels, torch.zeros_like(shift_labels))
+    count = valid.sum()
+    cfg = LossConfig(compute_entropy=False, cross_entropy=True)
+    prob = TokenLossProblem(logits, safe, valid.to(torch.float32), None, torch.clamp(count.to(torch.float32), min=1.0),
+                            None, None, cfg, scored_rows=logits.shape[1] - 1)
+    loss, _lp, _ent = _GrpoLoss.apply(logits, prob, inplace_backward)
+    return {"loss": loss, "token_count": count.to(torch.int32)}

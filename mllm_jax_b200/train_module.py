@@ -17,6 +17,27 @@ import torch
 from .ops import grpo_token_loss
 
 
+def per_sample_entropy_cuda(token_entropy: torch.Tensor, mask_loss: torch.Tensor):
+    """`entropy` and `entropy_loss` [B] through the library's kernel (mllm_grpo_entropy_stats)."""
+    import ctypes as C
+
+    from . import _lib
+
+    B, T = token_entropy.shape
+    dev = token_entropy.device
+    H = token_entropy.to(torch.float32).contiguous()
+    m = mask_loss.to(device=dev, dtype=torch.float32).contiguous()
+    out = torch.empty(2, B, dtype=torch.float32, device=dev)
+    a = _lib.GrpoArgs()
+    a.n_seqs, a.seq_rows, a.scored_rows, a.vocab, a.row_stride = B, T, T, 1, 1
+    a.temperature = 1.0
+    a.token_entropy, a.mask = H.data_ptr(), m.data_ptr()
+    a.sample_entropy, a.sample_entropy_window = out[0].data_ptr(), out[1].data_ptr()
+    with torch.cuda.device(dev):
+        _lib.call("mllm_grpo_entropy_stats", a, torch.cuda.current_stream().cuda_stream)
+    return out[0], out[1]
+
+
 def per_sample_entropy(token_entropy: torch.Tensor, mask_loss: torch.Tensor):
     """`entropy` and `entropy_loss` of the reference's return dict.
 
@@ -79,7 +100,7 @@ class TrainGRPOModule:
             temperature=self.temperature, epsilon_low=self.epsilon_low, epsilon_high=self.epsilon_high,
             beta=self.beta if ref_lp is not None else 0.0, softcap=self.softcap,
         )
-        entropy, entropy_loss = per_sample_entropy(out["token_entropy"], labels[:, 1:])
+        entropy, entropy_loss = per_sample_entropy_cuda(out["token_entropy"], labels[:, 1:])
         return {
             "loss": out["loss"],
             "per_token_logps": out["per_token_logps"].detach(),

@@ -157,6 +157,24 @@ def ppo_policy_call(logits: torch.Tensor, inputs: Mapping[str, Any], *, temperat
     return {"policy_loss": policy_loss, "entropy": entropy.detach(), "per_token_logps": per_token_logps.detach()}
 
 
+def sft_call(logits: torch.Tensor, inputs: Mapping[str, Any], *, label_ignore_id: int = -100,
+             dtype=torch.float32) -> dict:
+    """TrainSftModule.__call__ from the logits on (plugins/sft/jax/sft_module.py:29-45)."""
+    labels = inputs["labels"].long()
+    attention_mask = inputs["attention_mask"]
+    shift_logits = logits[:, :-1, :]                                          # :29
+    shift_labels = labels[:, 1:]                                              # :30
+    shift_attention = attention_mask[:, 1:]                                   # :31
+    valid = (shift_labels != int(label_ignore_id)) & shift_attention.bool()   # :33
+    safe_labels = torch.where(valid, shift_labels, torch.zeros_like(shift_labels))  # :34
+    log_probs = torch.log_softmax(shift_logits.to(dtype), dim=-1)             # :36
+    chosen = torch.gather(log_probs, -1, safe_labels[..., None])[..., 0]      # :37
+    per_token_loss = -chosen                                                  # :38
+    mask_f = valid.to(dtype)
+    loss = (per_token_loss * mask_f).sum() / torch.clamp(mask_f.sum(), min=1.0)  # _masked_mean, :10-13
+    return {"loss": loss, "token_count": valid.to(torch.int32).sum()}         # :41-45
+
+
 def analytic_rows(x: np.ndarray, chosen: np.ndarray, mask: np.ndarray, adv: np.ndarray,
                   old: Optional[np.ndarray], ref: Optional[np.ndarray], total_valid: float, *, beta: float = 0.0,
                   temperature: float = 1.0, epsilon_low: float = 0.2, epsilon_high: float = 0.3,

@@ -358,3 +358,44 @@ def test_full_size_workload_properties(cuda):
     assert_loss_close(out["loss"].item(), terms)
     # and the sampled terms match the oracle's
     assert np.allclose(out["problem"].loss_terms[rows.to(cuda)].cpu().numpy(), an["loss_terms"], atol=2e-3)
+
+
+def test_sft_cross_entropy(cuda):
+    """Masked causal-LM cross-entropy (the SFT plugin's loss) on the same kernels, against the oracle."""
+    B, L, V = 3, 21, 5000
+    logits, inputs = make_case(B, L, V, seed=45, old="none")
+    labels = inputs["input_ids"].clone().long()
+    labels[:, :5] = -100  # prompt positions are not supervised
+    att = torch.ones(B, L, dtype=torch.int32)
+    att[1, 15:] = 0  # padding
+    x = logits.float().requires_grad_(True)
+    ref = O.sft_call(x, {"labels": labels, "attention_mask": att})
+    ref["loss"].backward()
+    xg = logits.to(cuda).requires_grad_(True)
+    out = G.sft_cross_entropy(xg, inputs["input_ids"].to(cuda), labels.to(cuda), att.to(cuda))
+    out["loss"].backward()
+    assert int(out["token_count"]) == int(ref["token_count"])
+    assert_loss_close(out["loss"].item(), ref["loss"].item())
+    assert_dlogits_close(xg.grad, x.grad, what="sft cross-entropy")
+    # no supervised token at all: loss 0 and zero gradient (denominator clamps to 1)
+    none = torch.full_like(labels, -100)
+    xz = logits.to(cuda).requires_grad_(True)
+    z = G.sft_cross_entropy(xz, inputs["input_ids"].to(cuda), none.to(cuda), att.to(cuda))
+    z["loss"].backward()
+    assert z["loss"].item() == 0.0 and int(z["token_count"]) == 0 and (xz.grad == 0).all()
+
+
+@pytest.mark.parametrize("B,T", [(1, 1), (3, 7), (4, 130), (2, 5000)])
+def test_entropy_stats_kernel(cuda, B, T):
+    """Per-sample entropy monitors: the kernel against the host restatement of train_modules :141-157."""
+    from mllm_jax_b200.train_module import per_sample_entropy, per_sample_entropy_cuda
+
+    g = torch.Generator().manual_seed(46 + T)
+    H = torch.rand(B, T, generator=g) * 5
+    mask = (torch.rand(B, T, generator=g) < 0.7).to(torch.int32)
+    if B > 1:
+        mask[1] = 0  # a sample without valid tokens: 0/0
+    want = per_sample_entropy(H, mask)
+    got = per_sample_entropy_cuda(H.to(cuda), mask.to(cuda))
+    for w, gt in zip(want, got):
+        assert torch.allclose(gt.cpu(), w, atol=1e-5, rtol=1e-5, equal_nan=True)

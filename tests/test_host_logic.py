@@ -53,3 +53,29 @@ def test_sweep_workload_masks_half():
     w = synth.scaled(synth.sweep_workload(4096), vocab=64)
     a = synth.make_inputs(w)
     assert a["mask"].mean().item() == 0.5
+
+
+def test_ppo_update_collects_old_logps_in_first_epoch():
+    """Epoch 0 sees no old log-probs and its per_token_logps become the later epochs' old ones."""
+    from mllm_jax_b200.update import ppo_update
+
+    B, T = 8, 5
+    data = {"input_ids": torch.arange(B * (T + 1)).reshape(B, T + 1), "advantages": torch.arange(B).float()}
+    seen = []
+
+    def train_step(state, batch):
+        seen.append((state, "old_per_token_logps" in batch, batch["input_ids"][:, 0].tolist(),
+                     batch["total_valid_token_count"]))
+        lp = batch["input_ids"][:, 1:].float() * 0.5 + state
+        return state + 1, {"per_token_logps": lp, "entropy": torch.tensor(float(state)), "loss": torch.tensor(0.0)}
+
+    state, out, last, entropy = ppo_update(state=0, datas=data, total_valid_token_count=37, train_step=train_step,
+                                           grad_accum_steps=4, ppo_steps=3)
+    assert state == 12 and len(seen) == 12
+    assert [s[1] for s in seen] == [False] * 4 + [True] * 8
+    assert seen[1][2] == [12, 18] and all(s[3] == 37 for s in seen)
+    assert out["old_per_token_logps"].shape == (B, T)
+    expect = torch.cat([data["input_ids"][2 * i:2 * i + 2, 1:].float() * 0.5 + i for i in range(4)])
+    assert torch.equal(out["old_per_token_logps"], expect)
+    assert entropy.item() == 3.0 and last["entropy"].item() == 11.0
+    assert "old_per_token_logps" not in data  # the caller's dict is not modified

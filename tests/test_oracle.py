@@ -246,3 +246,16 @@ def test_golden_fixtures_match_oracle():
         assert abs(out["loss"].item() - float(z["loss"])) <= 2e-6 * max(1.0, abs(float(z["loss"]))), f
         assert np.allclose(out["token_entropy"].numpy(), z["token_entropy"], atol=5e-5), f
         assert np.allclose(out["dlogits"].numpy(), z["dlogits"], atol=1e-7, rtol=1e-4), f
+
+
+def test_sft_cross_entropy_known_answer():
+    """Uniform logits: every supervised token costs log V; unsupervised ones are ignored."""
+    B, L, V = 2, 6, 50
+    logits = torch.zeros(B, L, V, dtype=torch.bfloat16)
+    labels = torch.randint(0, V, (B, L))
+    labels[:, :2] = -100
+    att = torch.ones(B, L, dtype=torch.int32)
+    out = O.sft_call(logits, {"labels": labels, "attention_mask": att})
+    assert abs(out["loss"].item() - math.log(V)) < 1e-5 and int(out["token_count"]) == B * (L - 2)
+    empty = O.sft_call(logits, {"labels": torch.full((B, L), -100), "attention_mask": att})
+    assert empty["loss"].item() == 0.0
