@@ -154,6 +154,13 @@ int mllm_grpo_bwd(const mllm_grpo_args* args, void* stream);
  * training_step). */
 int mllm_grpo_fwd_bwd(const mllm_grpo_args* args, void* stream);
 
+/* Applies a late upstream cotangent to gradients that mllm_grpo_fwd_bwd already wrote with
+ * grad_scale = 1 (the forward of a custom_vjp that computes its gradient eagerly): dlogits *= g with
+ * g read from grad_scale_dev (or grad_scale).  Every CTA reads g first and returns at once when it is
+ * exactly 1, the case of jax.value_and_grad on the loss itself (update/train_step.py:24), so the
+ * common path moves no data.  Reads n_seqs, seq_rows, vocab, row_stride, dlogits, grad_scale(_dev). */
+int mllm_grpo_scale_grad(const mllm_grpo_args* args, void* stream);
+
 /* Vocabulary-sharded forward, step 1: per-token (max, sumexp, sum e*y,
  * chosen-logit-or-0) of this shard's columns -> partials[B*T, 4].  This is the
  * per-shard part of the all-reduce(max)/all-reduce(sum) XLA inserts when

@@ -20,7 +20,7 @@ EXPORTS = (
     "mllm_grpo_logprobs", "mllm_grpo_workspace_bytes", "mllm_grpo_abi_version", "mllm_grpo_status_string",
     "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count", "mllm_grpo_fwd_static_scratch",
     "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_exchange_bytes", "mllm_grpo_enable_peer_access",
-    "mllm_grpo_entropy_stats",
+    "mllm_grpo_entropy_stats", "mllm_grpo_scale_grad",
 )
 
 
@@ -70,7 +70,8 @@ def load():
     lib = C.CDLL(str(LIB_PATH))
     for name in ("mllm_grpo_fwd", "mllm_grpo_bwd", "mllm_grpo_fwd_bwd", "mllm_grpo_fwd_partials",
                  "mllm_grpo_combine", "mllm_grpo_logprobs", "mllm_grpo_fwd_static_scratch",
-                 "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_entropy_stats"):
+                 "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_entropy_stats",
+                 "mllm_grpo_scale_grad"):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(GrpoArgs), C.c_void_p]
         fn.restype = C.c_int

@@ -178,6 +178,15 @@ int mllm_grpo_fwd_bwd(const mllm_grpo_args* args, void* stream) {
   return MLLM_GRPO_OK;
 }
 
+int mllm_grpo_scale_grad(const mllm_grpo_args* args, void* stream) {
+  KernelParams k;
+  int st = validate(args, kDlogits, &k);
+  if (st) return st;
+  cudaError_t e = launch_scale_grad(k, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda(e);
+  return MLLM_GRPO_OK;
+}
+
 int mllm_grpo_fwd_partials(const mllm_grpo_args* args, void* stream) {
   KernelParams k;
   int st = validate(args, kLogits | kIds | kPartialsOut, &k);

@@ -16,6 +16,7 @@ cudaError_t launch_row_stats(const KernelParams& p, int mode, int ent, cudaStrea
 cudaError_t launch_combine(const KernelParams& p, int ent, cudaStream_t s);
 cudaError_t launch_loss_reduce(const KernelParams& p, cudaStream_t s);
 cudaError_t launch_dlogits(const KernelParams& p, cudaStream_t s);
+cudaError_t launch_scale_grad(const KernelParams& p, cudaStream_t s);
 // One-kernel forward+backward whose second read of a row is served by L2 (grpo_twopass.cu); long
 // rows are split over a cluster, and with sharded == true the vocabulary shards' partials are
 // exchanged over NVLink inside the kernel.  *taken is false (nothing launched) when logits and

@@ -172,6 +172,18 @@ __global__ void __launch_bounds__(256) dlogits_scalar_kernel(const KernelParams 
   }
 }
 
+// dlogits *= g for a cotangent that arrives after the gradient was written with g = 1; a no-op
+// (one scalar load per CTA) when g == 1.
+__global__ void __launch_bounds__(256) scale_grad_kernel(const KernelParams p) {
+  const float g = p.grad_scale_dev ? *p.grad_scale_dev : p.grad_scale;
+  if (g == 1.0f) return;
+  uint16_t* d16 = reinterpret_cast<uint16_t*>(p.dlogits + int64_t(blockIdx.x) * p.row_stride);
+  for (int64_t j = threadIdx.x; j < p.vocab; j += blockDim.x) {
+    const float v = __uint_as_float(uint32_t(d16[j]) << 16) * g;
+    d16[j] = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host-side launchers
 // ---------------------------------------------------------------------------------------------
@@ -211,6 +223,12 @@ cudaError_t launch_combine(const KernelParams& p, int ent, cudaStream_t s) {
     combine_kernel<0><<<grid, 256, 0, s>>>(p);
   else
     combine_kernel<1><<<grid, 256, 0, s>>>(p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scale_grad(const KernelParams& p, cudaStream_t s) {
+  scale_grad_kernel<<<static_cast<unsigned>(p.n_seqs * p.seq_rows), 256, 0, s>>>(p);
   count_launch();
   return cudaGetLastError();
 }

@@ -183,8 +183,15 @@ class _GrpoLoss(torch.autograd.Function):
     backward receives the scalar cotangent of the loss and streams the logits once more."""
 
     @staticmethod
-    def forward(ctx, logits, prob: TokenLossProblem, inplace_backward: bool):
-        prob.run("mllm_grpo_fwd")
+    def forward(ctx, logits, prob: TokenLossProblem, inplace_backward: bool, eager_grad: bool = False):
+        ctx.eager = bool(eager_grad) and logits.requires_grad
+        if ctx.eager:
+            # forward and gradient in one kernel (cotangent 1); backward applies a late cotangent, if any
+            prob.grad_scale = 1.0
+            prob.alloc_dlogits(inplace_backward)
+            prob.run("mllm_grpo_fwd_bwd")
+        else:
+            prob.run("mllm_grpo_fwd")
         ctx.prob = prob
         ctx.inplace = inplace_backward
         ctx.mark_non_differentiable(prob.per_token_logps)
@@ -196,9 +203,12 @@ class _GrpoLoss(torch.autograd.Function):
     def backward(ctx, grad_loss, _g_lp, _g_ent):
         prob: TokenLossProblem = ctx.prob
         prob.grad_scale_dev = grad_loss.to(torch.float32).reshape(1).contiguous()
+        if ctx.eager:
+            prob.run("mllm_grpo_scale_grad")  # returns at once on the device when the cotangent is 1
+            return prob.dlogits, None, None, None
         prob.alloc_dlogits(ctx.inplace)
         prob.run("mllm_grpo_bwd")
-        return prob.dlogits, None, None
+        return prob.dlogits, None, None, None
 
 
 def _shifted_side(input_ids: torch.Tensor, labels: torch.Tensor):
@@ -211,8 +221,12 @@ def grpo_token_loss(logits: torch.Tensor, input_ids: torch.Tensor, labels: torch
                     ref_per_token_logps: Optional[torch.Tensor] = None, *, temperature: float = 1.0,
                     epsilon_low: float = 0.2, epsilon_high: float = 0.3, beta: float = 0.0,
                     softcap: Optional[float] = None, compute_entropy: bool = True,
-                    inplace_backward: bool = False) -> dict:
+                    inplace_backward: bool = False, eager_grad: bool = False) -> dict:
     """GRPO token loss on the reference layout.
+
+    eager_grad=True computes dlogits together with the loss in one kernel (logits cross HBM once)
+    and lets backward() merely hand them over; a cotangent other than 1 is applied by one extra
+    in-place pass.  With inplace_backward=True that gradient overwrites the logits right away.
 
     logits [B, L, V] bf16, input_ids / labels [B, L], advantages [B] or [B, L-1],
     old/ref log-probs [B, L-1] or None.  Row i of a sequence is scored against
@@ -224,7 +238,7 @@ def grpo_token_loss(logits: torch.Tensor, input_ids: torch.Tensor, labels: torch
     ids, mask = _shifted_side(input_ids, labels)
     prob = TokenLossProblem(logits, ids, mask, advantages, total_valid_token_count, old_per_token_logps,
                             ref_per_token_logps, cfg, scored_rows=logits.shape[1] - 1)
-    loss, lp, ent = _GrpoLoss.apply(logits, prob, inplace_backward)
+    loss, lp, ent = _GrpoLoss.apply(logits, prob, inplace_backward, eager_grad)
     return {"loss": loss, "per_token_logps": lp, "token_entropy": ent if compute_entropy else None}
 
 

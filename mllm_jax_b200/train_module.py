@@ -76,6 +76,7 @@ class TrainGRPOModule:
     epsilon_high: float = 0.3
     entropy_threshold: float = 0.3
     softcap: Optional[float] = None
+    eager_grad: bool = True  # loss and dlogits from one kernel; backward() applies a late cotangent if any
 
     def __call__(self, inputs: Mapping[str, Any]) -> dict:
         from .ops import token_logprobs
@@ -98,7 +99,7 @@ class TrainGRPOModule:
             old_per_token_logps=inputs.get("old_per_token_logps"),
             ref_per_token_logps=ref_lp,
             temperature=self.temperature, epsilon_low=self.epsilon_low, epsilon_high=self.epsilon_high,
-            beta=self.beta if ref_lp is not None else 0.0, softcap=self.softcap,
+            beta=self.beta if ref_lp is not None else 0.0, softcap=self.softcap, eager_grad=self.eager_grad,
         )
         entropy, entropy_loss = per_sample_entropy_cuda(out["token_entropy"], labels[:, 1:])
         return {

@@ -399,3 +399,20 @@ def test_entropy_stats_kernel(cuda, B, T):
     got = per_sample_entropy_cuda(H.to(cuda), mask.to(cuda))
     for w, gt in zip(want, got):
         assert torch.allclose(gt.cpu(), w, atol=1e-5, rtol=1e-5, equal_nan=True)
+
+
+@pytest.mark.parametrize("scale", [1.0, -2.5])
+def test_eager_gradient_in_forward(cuda, scale):
+    """eager_grad: dlogits come out of the forward kernel; a late cotangent is applied in place."""
+    logits, inputs = make_case(3, 17, 4096, seed=47, old="wide", ref=True)
+    ref = O.reference_value_and_grad(logits, inputs, beta=0.04)
+    din = to_device(inputs, cuda)
+    x = logits.to(cuda).requires_grad_(True)
+    before = G.launch_count()
+    out = G.grpo_token_loss(x, din["input_ids"], din["labels"], din["advantages"], din["total_valid_token_count"],
+                            din["old_per_token_logps"], din["ref_per_token_logps"], beta=0.04, eager_grad=True)
+    (out["loss"] * scale).backward()
+    torch.cuda.synchronize()
+    assert G.launch_count() - before == 3  # two-pass kernel, loss reduction, cotangent check
+    assert_loss_close(out["loss"].item(), ref["loss"].item())
+    assert_dlogits_close(x.grad, scale * ref["dlogits"], what="eager")
