@@ -87,15 +87,40 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return d;
 }
 
-// Soft-cap y = cap*tanh(x/cap) as cap - 2cap/(1 + e^(2x/cap)): two SFU ops, absolute
-// error ~1e-7*cap (tanh.approx would be ~5e-4 relative, too coarse for a 2e-3 log-prob bound).
+// Soft-cap y = cap*tanh(x/cap) (deprecated/MLLM_JAX/language/gemma/transformer.py:337-339).
+// |x| <= cap (the common case: cap = 30 is 7.5 sigma of Gemma-like logits): an odd polynomial
+// y = x*P(x^2) of degree 11 evaluated on the FMA pipe, absolute error of tanh 3e-7 (1e-5 in y at
+// cap 30) -- one SFU op per element is then left for the softmax exponential.  Beyond the cap:
+// cap - 2cap/(1 + e^(2x/cap)), two SFU ops, exact at saturation.  (tanh.approx would be 5e-4
+// relative, too coarse for a 2e-3 log-prob bound.)
 struct SoftCap {
-  float c1;    // 2*log2(e)/cap
-  float cap;
-  __device__ __forceinline__ explicit SoftCap(float cap_) : c1(2.0f * kLog2e / cap_), cap(cap_) {}
-  // r = 1/(1+e^(2x/cap)); tanh = 1-2r; 1-tanh^2 = 4r(1-r)
-  __device__ __forceinline__ float r(float x) const { return rcpf(1.0f + ex2f(x * c1)); }
-  __device__ __forceinline__ float y(float x) const { return fmaf(-2.0f * cap, r(x), cap); }
+  float cap, icap, c1;
+  float d0, d1, d2, d3, d4, d5;  // tanh(z)/z ~ sum_k t_k z^(2k) on [-1, 1]; d_k = t_k / cap^(2k)
+  __device__ __forceinline__ explicit SoftCap(float cap_) : cap(cap_), icap(1.0f / cap_), c1(2.0f * kLog2e / cap_) {
+    const float i2 = icap * icap;
+    d0 = 0.9999968409538269f;
+    d1 = -0.3332400321960449f * i2;
+    d2 = 0.13253529369831085f * i2 * i2;
+    d3 = -0.05097292736172676f * i2 * i2 * i2;
+    d4 = 0.016114233061671257f * i2 * i2 * i2 * i2;
+    d5 = -0.0028394809924066067f * i2 * i2 * i2 * i2 * i2;
+  }
+  __device__ __forceinline__ float y_far(float x) const { return fmaf(-2.0f * cap, rcpf(1.0f + ex2f(x * c1)), cap); }
+  __device__ __forceinline__ float y(float x) const {
+    if (fabsf(x) > cap) return y_far(x);
+    const float q = x * x;
+    float p = fmaf(d5, q, d4);
+    p = fmaf(p, q, d3);
+    p = fmaf(p, q, d2);
+    p = fmaf(p, q, d1);
+    p = fmaf(p, q, d0);
+    return x * p;
+  }
+  // dy/dx = 1 - tanh^2 = 1 - (y/cap)^2
+  __device__ __forceinline__ float dydx(float y) const {
+    const float t = y * icap;
+    return fmaf(-t, t, 1.0f);
+  }
 };
 
 // Streaming accumulator of one thread.  ENT: 0 none, 1 entropy at temperature 1

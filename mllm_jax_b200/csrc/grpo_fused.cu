@@ -196,11 +196,10 @@ __global__ void __launch_bounds__(NT + 32, 1) fused_row_kernel(const KernelParam
             float x0 = bf16lo(w[k]), x1 = bf16hi(w[k]);
             float d0 = 1.f, d1 = 1.f;
             if (CAP) {
-              const float r0 = sc.r(x0), r1 = sc.r(x1);
-              x0 = fmaf(-2.0f * sc.cap, r0, sc.cap);
-              x1 = fmaf(-2.0f * sc.cap, r1, sc.cap);
-              d0 = 4.0f * r0 * (1.0f - r0);
-              d1 = 4.0f * r1 * (1.0f - r1);
+              x0 = sc.y(x0);
+              x1 = sc.y(x1);
+              d0 = sc.dydx(x0);
+              d1 = sc.dydx(x1);
             }
             const float p0 = ex2f(fmaf(x0, kLog2e, -mk)), p1 = ex2f(fmaf(x1, kLog2e, -mk));
             sS += p0;

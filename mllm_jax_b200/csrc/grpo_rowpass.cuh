@@ -248,12 +248,11 @@ __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, in
   auto one = [&](float x, int64_t j) -> float {  // scalar path: signed f32 result
     float d;
     if (CAP) {
-      const float rr = sc.r(x);
-      const float y = fmaf(-2.0f * sc.cap, rr, sc.cap);
+      const float y = sc.y(x);
       d = ex2f(fmaf(y, kLog2e, off));
       d = g < 0.f ? -d : d;
       if (j == cl) d -= g;
-      d *= 4.0f * rr * (1.0f - rr);
+      d *= sc.dydx(y);
     } else {
       d = ex2f(fmaf(x, kLog2e, off));
       d = g < 0.f ? -d : d;

@@ -160,9 +160,8 @@ __global__ void __launch_bounds__(256) dlogits_scalar_kernel(const KernelParams 
       const float x = __uint_as_float(uint32_t(x16[j]) << 16);
       float y = x, deriv = 1.f;
       if (CAP) {
-        const float rr = sc.r(x);
-        y = fmaf(-2.0f * sc.cap, rr, sc.cap);
-        deriv = 4.0f * rr * (1.0f - rr);
+        y = sc.y(x);
+        deriv = sc.dydx(y);
       }
       d = g * ex2f((y - lse) * kLog2e);
       if (j == cl) d -= g;
