@@ -87,6 +87,38 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return d;
 }
 
+// Packed fp32 pairs (Blackwell FFMA2/FMUL2/FADD2): two lanes of fp32 arithmetic per issue slot.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// Exact packed min of two bf16 pairs.
+__device__ __forceinline__ uint32_t bf16x2_min(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("min.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // Soft-cap y = cap*tanh(x/cap) (deprecated/MLLM_JAX/language/gemma/transformer.py:337-339).
 // |x| <= cap (the common case: cap = 30 is 7.5 sigma of Gemma-like logits): an odd polynomial
 // y = x*P(x^2) of degree 11 evaluated on the FMA pipe, absolute error of tanh 3e-7 (1e-5 in y at
@@ -115,6 +147,20 @@ struct SoftCap {
     p = fmaf(p, q, d1);
     p = fmaf(p, q, d0);
     return x * p;
+  }
+  // Both lanes of a pair at once; only valid when |x| <= cap in both lanes.
+  __device__ __forceinline__ f32x2 y2_near(f32x2 x) const {
+    const f32x2 q = mul2(x, x);
+    f32x2 p = fma2(pack2(d5, d5), q, pack2(d4, d4));
+    p = fma2(p, q, pack2(d3, d3));
+    p = fma2(p, q, pack2(d2, d2));
+    p = fma2(p, q, pack2(d1, d1));
+    p = fma2(p, q, pack2(d0, d0));
+    return mul2(x, p);
+  }
+  __device__ __forceinline__ f32x2 dydx2(f32x2 y) const {
+    const f32x2 t = mul2(y, pack2(icap, icap));
+    return fma2(mul2(y, pack2(-icap, -icap)), t, pack2(1.0f, 1.0f));
   }
   // dy/dx = 1 - tanh^2 = 1 - (y/cap)^2
   __device__ __forceinline__ float dydx(float y) const {

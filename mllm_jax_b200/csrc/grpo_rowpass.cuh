@@ -104,6 +104,43 @@ __device__ __forceinline__ void fold_vectors(RowAcc<ENT>& acc, const uint4 (&v)[
   if (mx > acc.m) acc.raise(mx, inv_temp);
   const float mk = acc.m * kLog2e;
   const float mk2 = mk * inv_temp;
+  if (CAP && ENT != 2) {
+    // Whole batch inside the cap (the common case): packed-pair polynomial tanh, two lanes per issue.
+    uint32_t mn2 = v[0].x;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      if (i) mn2 = bf16x2_min(mn2, v[i].x);
+      mn2 = bf16x2_min(mn2, v[i].y);
+      mn2 = bf16x2_min(mn2, v[i].z);
+      mn2 = bf16x2_min(mn2, v[i].w);
+    }
+    const float lo = fminf(bf16lo(mn2), bf16hi(mn2)), hi = fmaxf(bf16lo(mx2), bf16hi(mx2));
+    if (lo >= -sc.cap && hi <= sc.cap) {
+      const f32x2 kk = pack2(kLog2e, kLog2e), nmk = pack2(-mk, -mk);
+      f32x2 s2 = pack2(0.f, 0.f), u2 = pack2(0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const f32x2 y = sc.y2_near(pack2(bf16lo(w[j]), bf16hi(w[j])));
+          float t0, t1;
+          unpack2(fma2(y, kk, nmk), t0, t1);
+          const f32x2 p = pack2(ex2f(t0), ex2f(t1));
+          s2 = add2(s2, p);
+          if (ENT == 1) u2 = fma2(p, y, u2);
+        }
+      }
+      float a, b;
+      unpack2(s2, a, b);
+      acc.s += a + b;
+      if (ENT == 1) {
+        unpack2(u2, a, b);
+        acc.u += a + b;
+      }
+      return;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
@@ -278,11 +315,28 @@ __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, in
   auto do_vec = [&](const uint4& v, int64_t idx) -> uint4 {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
     uint32_t o[4];
+    bool near = false;
+    if (CAP && idx != cv) {
+      const uint32_t mx2 = bf16x2_max(bf16x2_max(w[0], w[1]), bf16x2_max(w[2], w[3]));
+      const uint32_t mn2 = bf16x2_min(bf16x2_min(w[0], w[1]), bf16x2_min(w[2], w[3]));
+      near = fminf(bf16lo(mn2), bf16hi(mn2)) >= -sc.cap && fmaxf(bf16lo(mx2), bf16hi(mx2)) <= sc.cap;
+    }
     if (!CAP && idx != cv) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float a = ex2f(fmaf(bf16lo(w[j]), kLog2e, off));
         const float c = ex2f(fmaf(bf16hi(w[j]), kLog2e, off));
+        o[j] = pack_bf16x2(a, c) ^ sgn;
+      }
+    } else if (CAP && near) {
+      // all eight inside the cap, chosen column elsewhere: packed-pair polynomial tanh
+      const f32x2 kk = pack2(kLog2e, kLog2e), oo = pack2(off, off);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const f32x2 y = sc.y2_near(pack2(bf16lo(w[j]), bf16hi(w[j])));
+        float t0, t1, a, c;
+        unpack2(fma2(y, kk, oo), t0, t1);
+        unpack2(mul2(pack2(ex2f(t0), ex2f(t1)), sc.dydx2(y)), a, c);
         o[j] = pack_bf16x2(a, c) ^ sgn;
       }
     } else {
