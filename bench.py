@@ -27,7 +27,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "fused GRPO loss fwd+bwd tokens/s"
-# DRAM bytes per logit element of two_pass_kernel, from profiles/two_pass_kernel_cfg1_launches_cfg0_ncu.md:
+# DRAM bytes per logit element of two_pass_kernel, from one ncu capture of the 2048-row case:
 # (623.2 + 564.8 + 57.5) MB / (2048 * 151936) elements = 4.003 (one bf16 read + one bf16 write).
 NCU_TRAFFIC_PER_ELEMENT = 4.003
 UNIT = "tokens/s"
@@ -295,7 +295,7 @@ def main():
                     "traffic": (NCU_TRAFFIC_PER_ELEMENT * v_local * N if (V == 151936 and mode == "auto") else None),
                     "traffic_note": "dram__bytes_read+write of one ncu capture on cfg0 (2048 rows, same V): 623.2 MB "
                                     "read + 564.8 MB written + 57.5 MB of gradient still dirty in L2, scaled by "
-                                    "rows (traffic grows in proportion); see profiles/",
+                                    "rows (traffic grows in proportion)",
                     "ms_per_launch": ms_k, "algorithmic_bytes_per_launch": bytes_step,
                     "note": "algorithmic = logits read twice + dlogits written once (6*V*N); the kernel's second "
                             "read is served by L2 and zero-gradient rows are not re-read, so its minimum DRAM "

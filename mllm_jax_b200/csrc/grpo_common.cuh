@@ -15,7 +15,6 @@
 namespace grpo {
 
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
 // Finite stand-in for "no element seen yet": its product with log2(e) stays finite.
 constexpr float kNegInit = -1.0e30f;
 

@@ -409,7 +409,6 @@ bool fused_supported(const KernelParams& p, int ent, fused::Plan* plan, fused::G
   if (p.vocab_start != 0 || p.vocab != p.vocab_total) return false;
   if ((p.vocab & 7) || (p.row_stride & 7)) return false;
   if ((reinterpret_cast<uintptr_t>(p.logits) & 15) || (reinterpret_cast<uintptr_t>(p.dlogits) & 15)) return false;
-  if (fused::env_int("MLLM_GRPO_DISABLE_FUSED", 0)) return false;
   const int64_t nvec = p.vocab / 8;
   const size_t avail = 232448 - sizeof(fused::Ctl) - 256;
   int want_cl = fused::env_int("MLLM_GRPO_FUSED_CLUSTER", 0);

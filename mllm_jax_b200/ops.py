@@ -11,14 +11,12 @@ Nothing here falls back to torch math or to the CPU.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Union
+from typing import Optional
 
 import torch
 
 from . import _lib
 from ._lib import GrpoArgs
-
-Number = Union[int, float]
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -27,10 +25,6 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
-
-
-def _f32(t: torch.Tensor) -> torch.Tensor:
-    return t.to(torch.float32).contiguous()
 
 
 @dataclass

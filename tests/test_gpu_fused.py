@@ -18,9 +18,9 @@ from tests.util import make_case, to_device
 
 pytestmark = pytest.mark.gpu
 
-ENV = ("MLLM_GRPO_FWD_BWD_MODE", "MLLM_GRPO_L2_CLUSTER", "MLLM_GRPO_L2_THREADS", "MLLM_GRPO_L2_CTAS",
+ENV = ("MLLM_GRPO_FWD_BWD_MODE", "MLLM_GRPO_L2_CLUSTER", "MLLM_GRPO_L2_THREADS",
        "MLLM_GRPO_FUSED_CLUSTER", "MLLM_GRPO_FUSED_THREADS", "MLLM_GRPO_FUSED_STAGES", "MLLM_GRPO_FUSED_CLUSTERS",
-       "MLLM_GRPO_DISABLE_FUSED")
+       )
 
 
 @pytest.fixture(autouse=True)
