@@ -314,8 +314,13 @@ def main():
                              "frac": bytes_step / (ms_per_step * 1e-3) / 1e9 / peak}}
 
     e2e = None
-    if not args.no_e2e and world == 1:
-        e2e = measure_e2e(G, data, cfg, dlogits, args, dev)
+    if not args.no_e2e:
+        if world == 1:
+            e2e = measure_e2e(data, lambda: G.grpo_value_and_grad(
+                data["logits"], data["token_ids"], data["mask"], data["advantages"], data["total_valid"],
+                data["old_logps"], data["ref_logps"], cfg=cfg, dlogits=dlogits), args)
+        else:
+            e2e = measure_e2e(data, step, args, dist, dev)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         del data, dlogits
@@ -339,9 +344,10 @@ def main():
         }))
 
 
-def measure_e2e(G, data, cfg, dlogits, args, dev):
-    """Same metric through the public API with HOST buffers: per step, copy the step's inputs from
-    pinned host memory, run fwd+bwd, read loss and per-token log-probs back."""
+def measure_e2e(data, step_fn, args, dist=None, dev=None):
+    """Same metric through the public API with HOST buffers: per step, copy the step's inputs (this
+    rank's shard when N > 1) from pinned host memory, run fwd+bwd through `step_fn`, read the loss and
+    the per-token log-probs back.  Time = max over ranks."""
     names = ("logits", "token_ids", "mask", "advantages", "old_logps", "ref_logps")
     host = {}
     try:
@@ -360,22 +366,32 @@ def measure_e2e(G, data, cfg, dlogits, args, dev):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for i in range(1 + steps):
         if i == 1:
+            if dist is not None:
+                dist.barrier()
             torch.cuda.synchronize()
             ev0.record()
         for k in names:
             data[k].copy_(host[k], non_blocking=True)
-        out = G.grpo_value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
-                                    data["total_valid"], data["old_logps"], data["ref_logps"], cfg=cfg,
-                                    dlogits=dlogits)
+        out = step_fn()
         lp_host.copy_(out["per_token_logps"], non_blocking=True)
         loss_host.copy_(out["loss"], non_blocking=True)
         torch.cuda.synchronize()
     ev1.record()
+    if dist is not None:
+        dist.barrier()
     torch.cuda.synchronize()
-    sec = ev0.elapsed_time(ev1) * 1e-3 / steps
-    return {"value": N / sec, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+    ms = ev0.elapsed_time(ev1)
+    world = 1
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        world = dist.get_world_size()
+    sec = ms * 1e-3 / steps
+    return {"value": N / sec, "unit": UNIT, "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
             "ms_per_step": sec * 1e3, "steps": steps,
-            "note": "logits cross PCIe every step; dlogits stay on the device for the lm_head backward"}
+            "note": "every rank copies its logits shard over its own PCIe link each step; dlogits stay on the "
+                    "device for the lm_head backward"}
 
 
 def run_reference(args):

@@ -247,7 +247,21 @@ cudaError_t launch_c(const KernelParams& p, int ent, int cluster, int threads, c
 // Cluster size and thread count for a row of `vocab` columns: slices of roughly 32-48 KB.
 void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, int* threads) {
   const int64_t row_bytes = p.vocab * 2;
-  int cl = row_bytes >= 192 * 1024 ? 8 : (row_bytes >= 96 * 1024 ? 4 : (row_bytes >= 56 * 1024 ? 2 : 1));
+  int cl = row_bytes >= 96 * 1024 ? 4 : (row_bytes >= 56 * 1024 ? 2 : 1);
+  if (row_bytes >= 192 * 1024) {
+    // 8 or 4 CTAs per row: take the split whose per-thread vector count leaves the smaller share to
+    // the one-vector-at-a-time remainder loop (128 threads, batches of 8).  Measured on one B200:
+    // V=151936 -> 8 (3.45 vs 3.54 ms), V=128256 -> 4 (12.4 vs 14.1 ms), V=256000 -> 4 (16.0 vs 16.6 ms).
+    double best = 2.0;
+    for (int c = 8; c >= 4; c /= 2) {
+      const double n = double((p.vocab / 8 + c - 1) / c) / 128.0;
+      const double singles = (n - 8.0 * double(int64_t(n / 8.0))) / n;
+      if (singles < best - 0.02) {
+        best = singles;
+        cl = c;
+      }
+    }
+  }
   // With the NVLink exchange in the kernel the split did not pay on 2 GPUs (152 KB row shards:
   // 1.99 ms unsplit, 2.01 ms CL=2, 2.06 ms CL=4): keep whole row shards per CTA.
   if (sharded) cl = 1;
