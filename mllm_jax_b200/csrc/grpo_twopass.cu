@@ -31,15 +31,17 @@ namespace grpo {
 constexpr unsigned long long kPeerWaitLimitNs = 2000000000ull;  // 2 s
 
 // One exchanged word: value bits in the low half, the epoch in the high half.
-__device__ __forceinline__ void st_word_sys(unsigned long long* p, float v, int epoch) {
-  const unsigned long long w = (static_cast<unsigned long long>(static_cast<uint32_t>(epoch)) << 32) |
-                               static_cast<unsigned long long>(__float_as_uint(v));
-  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+__device__ __forceinline__ unsigned long long make_word(float v, int epoch) {
+  return (static_cast<unsigned long long>(static_cast<uint32_t>(epoch)) << 32) |
+         static_cast<unsigned long long>(__float_as_uint(v));
 }
-__device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long long* p) {
-  unsigned long long w;
-  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
-  return w;
+// Two words per instruction; each 8-byte element is still its own atomic unit.
+__device__ __forceinline__ void st_words2_sys(unsigned long long* p, unsigned long long a, unsigned long long b) {
+  asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ void ld_words2_sys(const unsigned long long* p, unsigned long long& a,
+                                              unsigned long long& b) {
+  asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
 
 __device__ __forceinline__ void prefetch_l2(const void* p) {
@@ -125,32 +127,29 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
       if (rank == 0) {  // one CTA per row talks to the other GPUs
         const float4 mine = merge_partials(slots, CL);
         unsigned long long* dst = p.peer_words[tid] + (half + int64_t(me) * N + n) * 4;
-        st_word_sys(dst + 0, mine.x, p.exchange_epoch);
-        st_word_sys(dst + 1, mine.y, p.exchange_epoch);
-        st_word_sys(dst + 2, mine.z, p.exchange_epoch);
-        st_word_sys(dst + 3, mine.w, p.exchange_epoch);
+        st_words2_sys(dst, make_word(mine.x, p.exchange_epoch), make_word(mine.y, p.exchange_epoch));
+        st_words2_sys(dst + 2, make_word(mine.z, p.exchange_epoch), make_word(mine.w, p.exchange_epoch));
       }
-      // wait for rank `tid`'s partial of this row in OUR buffer
+      // wait for rank `tid`'s partial of this row in OUR buffer: all four words in one round trip
       const unsigned long long* src = p.peer_words[me] + (half + int64_t(tid) * N + n) * 4;
       const uint32_t want = static_cast<uint32_t>(p.exchange_epoch);
-      float got[4];
+      unsigned long long w0, w1, w2, w3;
       unsigned long long t0 = 0;
-      bool timed_out = false;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        unsigned long long w = ld_word_sys(src + i);
-        while (static_cast<uint32_t>(w >> 32) != want && !timed_out) {
-          if (t0 == 0) t0 = cl::globaltimer();
-          if (cl::globaltimer() - t0 > kPeerWaitLimitNs) {
-            timed_out = true;
-            if (p.device_status) atomicOr(p.device_status, MLLM_GRPO_DEV_WAIT_TIMEOUT);
-            break;
-          }
-          __nanosleep(32);
-          w = ld_word_sys(src + i);
+      for (;;) {
+        ld_words2_sys(src, w0, w1);
+        ld_words2_sys(src + 2, w2, w3);
+        if (static_cast<uint32_t>(w0 >> 32) == want && static_cast<uint32_t>(w1 >> 32) == want &&
+            static_cast<uint32_t>(w2 >> 32) == want && static_cast<uint32_t>(w3 >> 32) == want)
+          break;
+        if (t0 == 0) t0 = cl::globaltimer();
+        if (cl::globaltimer() - t0 > kPeerWaitLimitNs) {
+          if (p.device_status) atomicOr(p.device_status, MLLM_GRPO_DEV_WAIT_TIMEOUT);
+          break;
         }
-        got[i] = __uint_as_float(static_cast<uint32_t>(w));
+        __nanosleep(32);
       }
+      const float got[4] = {__uint_as_float(static_cast<uint32_t>(w0)), __uint_as_float(static_cast<uint32_t>(w1)),
+                            __uint_as_float(static_cast<uint32_t>(w2)), __uint_as_float(static_cast<uint32_t>(w3))};
       parts[tid] = make_float4(got[0], got[1], got[2], got[3]);
     }
   }
