@@ -157,3 +157,30 @@ class VocabParallelLoss:
         is re-read from L2 for the backward.  All ranks must call it the same number of times."""
         return self.step_fused(self.plan_fused(shard_logits, token_ids, mask, advantages, total_valid, old_logps,
                                                ref_logps, dlogits, grad_scale))
+
+
+class TokenParallelLoss:
+    """Rows split across ranks (the reference's real runs: batch over ("dp", "fsdp"), tp = 1,
+    plugins/training/runner/grpo_gsm8k.py:282).  `total_valid_token_count` is already global by contract
+    (:770), so each rank's loss is its share of the global loss and the only exchange is a scalar sum.
+    The gradient of a rank's rows needs no communication at all."""
+
+    def __init__(self, cfg: Optional[LossConfig] = None, group=None):
+        self.group = group
+        self.cfg = cfg or LossConfig()
+
+    def value_and_grad(self, local_logits, token_ids, mask, advantages, total_valid_global, old_logps=None,
+                       ref_logps=None, dlogits=None, reduce_loss: bool = True) -> dict:
+        from .ops import grpo_value_and_grad
+
+        out = grpo_value_and_grad(local_logits, token_ids, mask, advantages, total_valid_global, old_logps, ref_logps,
+                                  cfg=self.cfg, dlogits=dlogits)
+        out["local_loss"] = out["loss"]
+        if reduce_loss:
+            out["loss"] = self.reduce_loss(out["loss"])
+        return out
+
+    def reduce_loss(self, local_loss: torch.Tensor) -> torch.Tensor:
+        total = local_loss.detach().clone()
+        dist.all_reduce(total, op=dist.ReduceOp.SUM, group=self.group)
+        return total

@@ -416,3 +416,49 @@ def test_eager_gradient_in_forward(cuda, scale):
     assert G.launch_count() - before == 3  # two-pass kernel, loss reduction, cotangent check
     assert_loss_close(out["loss"].item(), ref["loss"].item())
     assert_dlogits_close(x.grad, scale * ref["dlogits"], what="eager")
+
+
+def test_minus_infinity_logits(cuda):
+    """Vocabulary entries masked with -inf: log-probs, loss and dlogits stay exact; only the entropy
+    monitor of such a row is not finite (0 * -inf in its sum), which is the documented limitation."""
+    B, L, V = 2, 6, 4096
+    logits, inputs = make_case(B, L, V, seed=48, old="none")
+    logits[:, :, 1000:1500] = float("-inf")
+    inputs["input_ids"] = inputs["input_ids"] % 1000  # chosen tokens are finite
+    ref = O.reference_value_and_grad(logits, inputs)
+    x = logits.to(cuda)
+    din = to_device(inputs, cuda)
+    for mode in ("auto", "sweeps"):
+        os.environ["MLLM_GRPO_FWD_BWD_MODE"] = mode
+        try:
+            out = G.grpo_value_and_grad(x, din["input_ids"], din["labels"], din["advantages"],
+                                        din["total_valid_token_count"], None, None, shifted=True)
+        finally:
+            os.environ.pop("MLLM_GRPO_FWD_BWD_MODE", None)
+        assert (out["per_token_logps"].cpu() - ref["per_token_logps"]).abs().max() <= LP_ATOL
+        assert_loss_close(out["loss"].item(), ref["loss"].item())
+        assert_dlogits_close(out["dlogits"], ref["dlogits"], what=f"-inf logits {mode}")
+        assert (out["dlogits"][:, :, 1000:1500] == 0).all()
+
+
+def test_extreme_logits_and_tiny_vocab(cuda):
+    """bf16 extremes (+-3e38 entries, a 1e4 spike) and a one-column vocabulary."""
+    B, L, V = 1, 5, 256
+    logits, inputs = make_case(B, L, V, seed=49, old="none", mask_kind="ones")
+    logits[0, 0, 3] = 1.0e4
+    logits[0, 1, 7] = -3.0e38
+    logits[0, 2, :] = -3.0e38
+    logits[0, 2, 5] = 3.0e38
+    ref = O.reference_value_and_grad(logits, inputs)
+    out = G.grpo_value_and_grad(logits.to(cuda), inputs["input_ids"].to(cuda), inputs["labels"].to(cuda),
+                                inputs["advantages"].to(cuda), inputs["total_valid_token_count"], shifted=True)
+    finite = torch.isfinite(ref["per_token_logps"])
+    assert torch.equal(torch.isfinite(out["per_token_logps"].cpu()), finite)
+    assert (out["per_token_logps"].cpu()[finite] - ref["per_token_logps"][finite]).abs().max() <= LP_ATOL
+    # one column: log-prob 0, entropy 0, zero gradient
+    one = torch.randn(2, 4, 1).to(torch.bfloat16)
+    ids = torch.zeros(2, 4, dtype=torch.int32)
+    o1 = G.grpo_value_and_grad(one.to(cuda), ids.to(cuda), torch.ones(2, 4, dtype=torch.int32).to(cuda),
+                               torch.tensor([1.0, -1.0]).to(cuda), 6.0, shifted=True)
+    assert o1["per_token_logps"].abs().max() == 0 and o1["token_entropy"].abs().max() == 0
+    assert (o1["dlogits"] == 0).all() and o1["loss"].item() == 0.0

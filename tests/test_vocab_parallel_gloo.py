@@ -41,6 +41,10 @@ def _worker(rank, world, port, ret):
         lp = P[:, :, 3].sum(axis=0) - (M + np.log(S))
         ref = O.reference_call(logits, inputs)["per_token_logps"].numpy().reshape(-1)
         ret[rank] = float(np.abs(lp - ref).max())
+        # token-parallel: the global loss is the plain sum of the ranks' losses
+        from mllm_jax_b200.vocab_parallel import TokenParallelLoss
+        total = TokenParallelLoss().reduce_loss(torch.tensor(float(rank + 1)))
+        assert total.item() == sum(range(1, world + 1))
         # a mismatched buffer is refused before any communication
         try:
             exchange_partials(mine, out=torch.empty(world, N + 1, 4))
