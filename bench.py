@@ -207,17 +207,28 @@ def main():
 
         call_args = (data["logits"], data["token_ids"], data["mask"], data["advantages"], data["total_valid"],
                      data["old_logps"], data["ref_logps"])
-        if args.vp_mode == "fused":
-            # buffers bound once (static shapes), every step relaunches on the same addresses
-            plan = vp.plan_fused(*call_args, dlogits=dlogits)
-
+        vp_mode, vp_note = args.vp_mode, None
+        if vp_mode == "fused":
+            try:
+                # buffers bound once (static shapes), every step relaunches on the same addresses
+                plan = vp.plan_fused(*call_args, dlogits=dlogits)
+                ok = torch.ones(1, device=dev)
+            except Exception as exc:  # symmetric memory unavailable on this box
+                vp_note = f"peer exchange buffers could not be set up ({type(exc).__name__}: {str(exc)[:80]})"
+                ok = torch.zeros(1, device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 0:
+                vp_mode = "nccl"
+                vp_note = vp_note or "another rank could not set up the peer exchange buffers"
+        if vp_mode == "fused":
             def step():
                 return vp.step_fused(plan)
         else:
             def step():
                 return vp.value_and_grad(*call_args, dlogits=dlogits)
         parallelism = f"vocab-parallel tp{world}, exchange: " + (
-            "peer stores inside the kernel" if args.vp_mode == "fused" else "NCCL all-gather between kernels")
+            "peer stores inside the kernel" if vp_mode == "fused" else "NCCL all-gather between kernels") + (
+            f" [{vp_note}]" if vp_note else "")
 
     def barrier():
         if dist is not None:
