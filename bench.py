@@ -301,7 +301,7 @@ def main():
         ms_k = sum(t_s) / len(t_s)
         mode = os.environ.get("MLLM_GRPO_FWD_BWD_MODE", "auto")
         ach = bytes_step / (ms_k * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": f"single-kernel fwd+bwd (mode {mode}: row_two_pass_cluster_kernel)",
+        roofline = {"bound": "hbm", "kernel": f"single-kernel fwd+bwd (mode {mode}: two_pass_kernel)",
                     "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": peak_kind,
                     "traffic": (NCU_TRAFFIC_PER_ELEMENT * v_local * N if (V == 151936 and mode == "auto") else None),
                     "traffic_note": "dram__bytes_read+write of one ncu capture on cfg0 (2048 rows, same V): 623.2 MB "
