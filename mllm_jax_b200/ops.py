@@ -147,6 +147,15 @@ class TokenLossProblem:
         a.total_valid_dev, a.grad_scale_dev = _ptr(self.total_valid_dev), _ptr(self.grad_scale_dev)
         a.per_token_logps, a.token_entropy = _ptr(self.per_token_logps), _ptr(self.token_entropy)
         a.lse, a.grad_coef, a.loss, a.loss_terms = _ptr(self.lse), _ptr(self.grad_coef), _ptr(self.loss), _ptr(self.loss_terms)
+        if self.dlogits is not None and (self.dlogits.shape != self.logits.shape or
+                                         self.dlogits.stride() != self.logits.stride() or
+                                         self.dlogits.dtype != torch.bfloat16 or
+                                         self.dlogits.device != self.logits.device):
+            # one row stride serves both buffers in the kernels: a differently laid out gradient buffer
+            # would be written out of bounds
+            raise ValueError("dlogits must match logits in shape, strides, dtype and device "
+                             f"(logits {tuple(self.logits.shape)}/{self.logits.stride()}, "
+                             f"dlogits {tuple(self.dlogits.shape)}/{self.dlogits.stride()})")
         a.dlogits = _ptr(self.dlogits)
         a.partials, a.gathered_partials, a.n_shards = _ptr(self.partials), _ptr(self.gathered), self.n_shards
         a.device_status = _ptr(self.device_status)
@@ -157,7 +166,12 @@ class TokenLossProblem:
         return a
 
     def alloc_dlogits(self, inplace: bool = False) -> torch.Tensor:
-        self.dlogits = self.logits if inplace else torch.empty_like(self.logits)
+        """Gradient buffer with exactly the strides of the logits (also for strided views)."""
+        if inplace:
+            self.dlogits = self.logits
+        else:
+            self.dlogits = torch.empty_strided(self.logits.shape, self.logits.stride(), dtype=self.logits.dtype,
+                                               device=self.logits.device)
         return self.dlogits
 
     def run(self, entry: str, reuse_args: bool = False) -> None:

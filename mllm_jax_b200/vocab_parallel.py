@@ -129,10 +129,11 @@ class VocabParallelLoss:
                 "dlogits": d, "problem": p}
 
     def plan_fused(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None, ref_logps=None,
-                   dlogits=None, grad_scale: float = 1.0) -> TokenLossProblem:
+                   dlogits=None, grad_scale: float = 1.0, scored_rows: Optional[int] = None) -> TokenLossProblem:
         """Bind buffers once for repeated fused steps on the same addresses (static shapes, new
-        contents each step): `step_fused(plan)` then only bumps the epoch and launches."""
-        p = self.problem(shard_logits, token_ids, mask, advantages, total_valid, old_logps, ref_logps)
+        contents each step): `step_fused(plan)` then only bumps the epoch and launches.
+        scored_rows = L - 1 takes the reference layout (row i scored against token i + 1, side arrays [B, L-1])."""
+        p = self.problem(shard_logits, token_ids, mask, advantages, total_valid, old_logps, ref_logps, scored_rows)
         if self._peer is None or self._peer.n_tokens != p.N:
             self._peer = PeerExchange(p.N, shard_logits.device, self.group)
         p.peer_ptrs, p.shard_rank, p.n_shards = self._peer.ptrs, self.rank, self.world
@@ -151,12 +152,13 @@ class VocabParallelLoss:
                 "dlogits": p.dlogits, "problem": p}
 
     def value_and_grad_fused(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None,
-                             ref_logps=None, dlogits=None, grad_scale: float = 1.0) -> dict:
+                             ref_logps=None, dlogits=None, grad_scale: float = 1.0,
+                             scored_rows: Optional[int] = None) -> dict:
         """Same result as value_and_grad through ONE kernel per GPU (mllm_grpo_fwd_bwd_sharded): the
         per-token partials cross NVLink as peer stores issued by the kernel itself, and the row shard
         is re-read from L2 for the backward.  All ranks must call it the same number of times."""
         return self.step_fused(self.plan_fused(shard_logits, token_ids, mask, advantages, total_valid, old_logps,
-                                               ref_logps, dlogits, grad_scale))
+                                               ref_logps, dlogits, grad_scale, scored_rows))
 
 
 class TokenParallelLoss:

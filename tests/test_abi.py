@@ -112,3 +112,26 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         _lib.load()
+
+
+def test_gradient_buffer_layout_is_checked_on_the_host():
+    """A gradient buffer whose strides differ from the logits' would be written out of bounds: refused."""
+    import torch
+
+    from mllm_jax_b200.ops import LossConfig, TokenLossProblem
+
+
+    logits = torch.zeros(2, 3, 16, dtype=torch.bfloat16)
+    prob = TokenLossProblem.__new__(TokenLossProblem)
+    prob.logits = logits[:, :, :8]
+    prob.dlogits = torch.zeros(2, 3, 8, dtype=torch.bfloat16)
+    prob.B, prob.L, prob.T, prob.V, prob.row_stride = 2, 3, 3, 8, 16
+    prob.vocab_start, prob.vocab_total, prob.cfg = 0, 8, LossConfig()
+    prob.adv_per_token, prob.grad_scale, prob.total_valid = 0, 1.0, 1.0
+    for name in ("chosen_ids", "mask", "advantages", "old_logps", "ref_logps", "total_valid_dev", "grad_scale_dev",
+                 "per_token_logps", "token_entropy", "lse", "grad_coef", "loss", "loss_terms", "partials", "gathered",
+                 "device_status", "peer_ptrs"):
+        setattr(prob, name, None)
+    prob.n_shards = prob.shard_rank = prob.exchange_epoch = 0
+    with pytest.raises(ValueError, match="dlogits must match logits"):
+        prob.args()

@@ -48,7 +48,12 @@ def _run_rank(rank, world, port, ret):
         outs = {"nccl": vp.value_and_grad(*args) if world > 1 else None}
         for i in range(3):  # three fused calls in a row: both epoch parities, no barrier between them
             outs[f"fused{i}"] = vp.value_and_grad_fused(*args, dlogits=torch.empty_like(shard))
+        # the reference layout on a strided shard view: L rows per sequence, L-1 scored, last row zero
+        full = logits.to(dev)[:, :, vp.start:vp.stop]
+        shifted = vp.value_and_grad_fused(full, *args[1:], scored_rows=L - 1)  # gradient buffer with the view's strides
         torch.cuda.synchronize()
+        assert_dlogits_close(shifted["dlogits"], ref["dlogits"][:, :, vp.start:vp.stop], what="shifted shard view")
+        assert (shifted["per_token_logps"].cpu() - ref["per_token_logps"]).abs().max() <= LP_ATOL
         for name, out in outs.items():
             if out is None:
                 continue
