@@ -462,3 +462,31 @@ def test_extreme_logits_and_tiny_vocab(cuda):
                                torch.tensor([1.0, -1.0]).to(cuda), 6.0, shifted=True)
     assert o1["per_token_logps"].abs().max() == 0 and o1["token_entropy"].abs().max() == 0
     assert (o1["dlogits"] == 0).all() and o1["loss"].item() == 0.0
+
+
+@pytest.mark.parametrize("name,rows", [("cfg2", 4), ("cfg3", 2)])
+def test_other_config_shapes_sampled_rows(cuda, name, rows):
+    """Llama-3 (V=128256) and Gemma-2 (V=256000, soft-cap 30, logits ~ N(0, 4^2)) shapes at a few
+    thousand rows: sampled rows against the closed-form oracle, zero rows exactly zero."""
+    w = synth.scaled(synth.CONFIGS[name], n_seqs=rows)
+    data = synth.make_inputs(w, seed=3, device="cuda")
+    cfg = G.LossConfig(epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high, beta=w.beta, softcap=w.softcap)
+    out = G.grpo_value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
+                                data["total_valid"], data["old_logps"], data["ref_logps"], cfg=cfg)
+    torch.cuda.synchronize()
+    N, V = w.n_tokens, w.vocab
+    d = out["dlogits"].view(N, V)
+    mask = data["mask"].view(N)
+    gen = torch.Generator().manual_seed(11)
+    rows_idx = torch.cat([torch.tensor([0, N - 1]), torch.randint(0, N, (126,), generator=gen)]).unique().to(cuda)
+    x = data["logits"].view(N, V)[rows_idx].double().cpu().numpy()
+    advN = data["advantages"][:, None].expand(w.n_seqs, w.seq_len).reshape(N)
+    pick = lambda t: t.reshape(N)[rows_idx].double().cpu().numpy()  # noqa: E731
+    an = O.analytic_rows(x, data["token_ids"].reshape(N)[rows_idx].long().cpu().numpy(), pick(mask), pick(advN),
+                         pick(data["old_logps"]), pick(data["ref_logps"]), data["total_valid"], beta=w.beta,
+                         epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high, softcap=w.softcap)
+    assert np.abs(pick(out["per_token_logps"]) - an["lp"]).max() <= LP_ATOL
+    assert np.abs(pick(out["token_entropy"]) - an["entropy_guard"]).max() <= ENT_ATOL
+    assert_dlogits_close(d[rows_idx], torch.from_numpy(an["dlogits"]), what=f"{name} sampled rows")
+    zero = (mask == 0).nonzero()[:64, 0]
+    assert (d[zero] == 0).all()
