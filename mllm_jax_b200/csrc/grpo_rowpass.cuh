@@ -73,10 +73,19 @@ __device__ __forceinline__ void stg_hint(uint4* p, const uint4& v, uint64_t pol)
                : "memory");
 }
 // LD: 0 read-only streaming load, 1 coherent streaming load, 2 load with an L2 policy.
+// LD 3: the row slice sits in shared memory (landed there by a bulk copy).
+__device__ __forceinline__ uint4 lds_row(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(p))));
+  return v;
+}
 template <int LD>
 __device__ __forceinline__ uint4 ld_row(const uint4* p, uint64_t pol) {
   if (LD == 0) return ldg_stream(p);
   if (LD == 1) return ldg_stream_rw(p);
+  if (LD == 3) return lds_row(p);
   return ldg_hint(p, pol);
 }
 template <int LD>
@@ -262,7 +271,8 @@ __device__ __forceinline__ float chosen_logit(const KernelParams& p, int64_t n, 
 
 // Second streaming pass over one row: dlogits = g*(softmax - onehot) (times dy/dx with the soft-cap)
 // in bf16.  g == 0 writes exact zeros without reading the logits.
-template <int THREADS, int UNROLL, bool CAP, int LD>
+// LDSRC: load flavour of the source row when it differs from the store flavour LD (3 = shared memory).
+template <int THREADS, int UNROLL, bool CAP, int LD, int LDSRC = -1>
 __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, int64_t V, float g, float lse,
                                           int64_t cl, const SoftCap& sc, uint64_t pol) {
   const int tid = threadIdx.x;
@@ -351,7 +361,8 @@ __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, in
     return make_uint4(o[0], o[1], o[2], o[3]);
   };
 
-  constexpr int LDX = (LD == 0) ? 1 : LD;  // never the non-coherent path: the output may alias the input
+  // never the non-coherent path: the output may alias the input
+  constexpr int LDX = LDSRC >= 0 ? LDSRC : ((LD == 0) ? 1 : LD);
   int64_t i = tid;
   constexpr int64_t kStep = int64_t(UNROLL) * THREADS;
   for (; i + kStep - THREADS < sp.nvec; i += kStep) {

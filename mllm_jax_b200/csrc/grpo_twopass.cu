@@ -62,8 +62,13 @@ __device__ __forceinline__ float4 merge_partials(const float4* parts, int count)
   return make_float4(M, S, U, yc);
 }
 
-template <int CL, int THREADS, int UNROLL, int ENT, bool CAP, bool SHARDED>
+// SMEM: the CTA's row slice is brought into shared memory by one bulk (TMA) copy and both passes read
+// it from there: no load registers, the whole slice in flight at once, and no second trip to L2.
+template <int CL, int THREADS, int UNROLL, int ENT, bool CAP, bool SHARDED, bool SMEM>
 __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p, const int64_t vec_per) {
+  extern __shared__ __align__(128) unsigned char slice_smem[];
+  __shared__ unsigned long long load_bar;
+  __shared__ int abort_flag;
   __shared__ float red[160];
   __shared__ float bc[2];
   __shared__ __align__(16) float4 slots[8];  // cluster slices' partials
@@ -89,6 +94,14 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
   }
   // Tell the cluster peers this CTA is running (its shared memory exists) without blocking yet.
   if (CL > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  if (SMEM && tid == 0) {
+    abort_flag = 0;
+    const uint32_t bar = cl::smem_u32(&load_bar);
+    cl::mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    cl::mbar_expect_tx(bar, uint32_t(ncol) * 2u);
+    cl::bulk_load(cl::smem_u32(slice_smem), x16, uint32_t(ncol) * 2u, bar);
+  }
   const int64_t n = b * p.scored_rows + t;
   // Everything the epilogue needs is requested before the first pass, so its latency is hidden.
   int64_t c = p.chosen_ids[n];
@@ -106,7 +119,13 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
     if (p.ref_logps) prefetch_l2(p.ref_logps + n);
   }
 
-  const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, 2>(x16, ncol, p.inv_temperature, sc, red, keep);
+  const uint16_t* xs = x16;
+  if (SMEM) {
+    __syncthreads();  // the barrier is initialised
+    cl::mbar_wait(cl::smem_u32(&load_bar), 0, &abort_flag, p.device_status);  // bounded
+    xs = reinterpret_cast<const uint16_t*>(slice_smem);
+  }
+  const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, SMEM ? 3 : 2>(xs, ncol, p.inv_temperature, sc, red, keep);
   if (CAP && tid < 8 && cl_local >= 0 && cl_local < ncol) yc_own = sc.y(yc_own);
 
   if (CL > 1) {
@@ -176,7 +195,7 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
     bc[1] = o.lse;
   }
   __syncthreads();
-  row_pass2<THREADS, UNROLL, CAP, 2>(x16, d16, ncol, bc[0], bc[1], cl_local, sc, drop);
+  row_pass2<THREADS, UNROLL, CAP, 2, SMEM ? 3 : -1>(xs, d16, ncol, bc[0], bc[1], cl_local, sc, drop);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -185,12 +204,24 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
 namespace {
 
 template <int CL, int THREADS, int UNROLL, int ENT, bool CAP, bool SHARDED>
-cudaError_t launch_k(const KernelParams& p, cudaStream_t s) {
+cudaError_t launch_k(const KernelParams& p, bool smem, cudaStream_t s) {
   const int64_t R = p.n_seqs * p.seq_rows;
   const int64_t nvec = p.vocab / 8;
   const int64_t per = (nvec + CL - 1) / CL;
-  auto kern = two_pass_kernel<CL, THREADS, UNROLL, ENT, CAP, SHARDED>;
+  const size_t slice_bytes = size_t(CL > 1 ? per : nvec) * 16;
+  // shared-memory loads are short: batches of 2 vectors keep the register count low
+  auto kern = two_pass_kernel<CL, THREADS, UNROLL, ENT, CAP, SHARDED, false>;
+  if constexpr (CL == 1 && ENT != 2) {  // only unsplit rows are staged (split ones measured slower)
+    if (smem) kern = two_pass_kernel<1, THREADS, 2, ENT, CAP, SHARDED, true>;
+  } else {
+    smem = false;
+  }
+  const size_t dyn = smem ? slice_bytes : 0;
   cudaError_t e;
+  if (smem && dyn > 48 * 1024) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (e != cudaSuccess) return e;
+  }
   if (CL > 1) {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
@@ -200,13 +231,13 @@ cudaError_t launch_k(const KernelParams& p, cudaStream_t s) {
     attr[0].val.clusterDim.z = 1;
     cfg.gridDim = dim3(static_cast<unsigned>(R * CL), 1, 1);
     cfg.blockDim = dim3(THREADS, 1, 1);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = dyn;
     cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, kern, p, per);
   } else {
-    kern<<<static_cast<unsigned>(R), THREADS, 0, s>>>(p, per);
+    kern<<<static_cast<unsigned>(R), THREADS, dyn, s>>>(p, per);
     e = cudaGetLastError();
   }
   count_launch();
@@ -214,37 +245,37 @@ cudaError_t launch_k(const KernelParams& p, cudaStream_t s) {
 }
 
 template <int CL, int THREADS, int UNROLL, bool SHARDED>
-cudaError_t launch_e(const KernelParams& p, int ent, cudaStream_t s) {
+cudaError_t launch_e(const KernelParams& p, int ent, bool smem, cudaStream_t s) {
   const bool cap = p.softcap > 0.f;
-  if (ent == 0) return cap ? launch_k<CL, THREADS, UNROLL, 0, true, SHARDED>(p, s) : launch_k<CL, THREADS, UNROLL, 0, false, SHARDED>(p, s);
-  if (ent == 1) return cap ? launch_k<CL, THREADS, UNROLL, 1, true, SHARDED>(p, s) : launch_k<CL, THREADS, UNROLL, 1, false, SHARDED>(p, s);
+  if (ent == 0) return cap ? launch_k<CL, THREADS, UNROLL, 0, true, SHARDED>(p, smem, s) : launch_k<CL, THREADS, UNROLL, 0, false, SHARDED>(p, smem, s);
+  if (ent == 1) return cap ? launch_k<CL, THREADS, UNROLL, 1, true, SHARDED>(p, smem, s) : launch_k<CL, THREADS, UNROLL, 1, false, SHARDED>(p, smem, s);
   if (CL == 1 && !SHARDED)
-    return cap ? launch_k<1, THREADS, UNROLL, 2, true, false>(p, s) : launch_k<1, THREADS, UNROLL, 2, false, false>(p, s);
+    return cap ? launch_k<1, THREADS, UNROLL, 2, true, false>(p, false, s) : launch_k<1, THREADS, UNROLL, 2, false, false>(p, false, s);
   return cudaErrorInvalidValue;
 }
 
 template <int CL, bool SHARDED>
-cudaError_t launch_t(const KernelParams& p, int ent, int threads, cudaStream_t s) {
-  if (threads <= 64 && CL == 1) return launch_e<1, 64, 8, SHARDED>(p, ent, s);
-  if (threads <= 128) return launch_e<CL, 128, 8, SHARDED>(p, ent, s);
-  if (threads <= 256 || CL > 1) return launch_e<CL, 256, 4, SHARDED>(p, ent, s);
-  return launch_e<CL, 512, 4, SHARDED>(p, ent, s);
+cudaError_t launch_t(const KernelParams& p, int ent, int threads, bool smem, cudaStream_t s) {
+  if (threads <= 64 && CL == 1) return launch_e<1, 64, 8, SHARDED>(p, ent, smem, s);
+  if (threads <= 128) return launch_e<CL, 128, 8, SHARDED>(p, ent, smem, s);
+  if (threads <= 256 || CL > 1) return launch_e<CL, 256, 4, SHARDED>(p, ent, smem, s);
+  return launch_e<CL, 512, 4, SHARDED>(p, ent, smem, s);
 }
 
 template <bool SHARDED>
-cudaError_t launch_c(const KernelParams& p, int ent, int cluster, int threads, cudaStream_t s) {
+cudaError_t launch_c(const KernelParams& p, int ent, int cluster, int threads, bool smem, cudaStream_t s) {
   switch (cluster) {
-    case 1: return launch_t<1, SHARDED>(p, ent, threads, s);
-    case 2: return launch_t<2, SHARDED>(p, ent, threads, s);
-    case 4: return launch_t<4, SHARDED>(p, ent, threads, s);
-    default: return launch_t<8, SHARDED>(p, ent, threads, s);
+    case 1: return launch_t<1, SHARDED>(p, ent, threads, smem, s);
+    case 2: return launch_t<2, SHARDED>(p, ent, threads, smem, s);
+    case 4: return launch_t<4, SHARDED>(p, ent, threads, smem, s);
+    default: return launch_t<8, SHARDED>(p, ent, threads, smem, s);
   }
 }
 
 }  // namespace
 
 // Cluster size and thread count for a row of `vocab` columns: slices of roughly 32-48 KB.
-void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, int* threads) {
+void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, int* threads, bool* smem) {
   const int64_t row_bytes = p.vocab * 2;
   int cl = row_bytes >= 96 * 1024 ? 4 : (row_bytes >= 56 * 1024 ? 2 : 1);
   if (row_bytes >= 192 * 1024) {
@@ -277,8 +308,17 @@ void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, i
   const char* env_th = std::getenv("MLLM_GRPO_L2_THREADS");
   // measured on one B200 (unsplit rows): 38 KB rows 64 threads, 76 KB 256, 152 KB and longer 512
   int th = env_th ? std::atoi(env_th) : (cl > 1 ? 128 : (row_bytes < 56 * 1024 ? 64 : (row_bytes < 112 * 1024 || sharded ? 256 : 512)));
+  // Rows of at most 48 KB that are not split: stage the row in shared memory with one bulk (TMA) copy
+  // and run both passes from there (38 KB rows on one B200: 0.400 ms against 0.452 ms through
+  // registers).  Longer rows and cluster slices measured slower that way (too few CTAs per SM).
+  const size_t slice_bytes = size_t(cl > 1 ? (nvec + cl - 1) / cl : nvec) * 16;
+  bool sm = cl == 1 && aligned16 && ent != 2 && slice_bytes <= 48 * 1024 && slice_bytes >= 4096;
+  const char* env_sm = std::getenv("MLLM_GRPO_SMEM");
+  if (env_sm) sm = std::atoi(env_sm) != 0 && cl == 1 && aligned16 && ent != 2 && slice_bytes <= 100 * 1024;
+  if (sm && !env_th) th = 256;
   *cluster = cl;
   *threads = th;
+  *smem = sm;
 }
 
 // *taken is false (nothing launched) when logits and dlogits rows do not share their 16-byte phase.
@@ -287,8 +327,9 @@ cudaError_t launch_two_pass(const KernelParams& p, int ent, bool sharded, cudaSt
   *taken = ((ax ^ ad) & 15) == 0;
   if (!*taken) return cudaSuccess;
   int cluster = 1, threads = 256;
-  two_pass_plan(p, ent, sharded, &cluster, &threads);
-  return sharded ? launch_c<true>(p, ent, cluster, threads, s) : launch_c<false>(p, ent, cluster, threads, s);
+  bool smem = false;
+  two_pass_plan(p, ent, sharded, &cluster, &threads, &smem);
+  return sharded ? launch_c<true>(p, ent, cluster, threads, smem, s) : launch_c<false>(p, ent, cluster, threads, smem, s);
 }
 
 }  // namespace grpo
