@@ -1,5 +1,7 @@
 // Forward AND backward of the GRPO token loss in one kernel: each logits row (or this rank's column
-// shard of it) is streamed twice by the same CTAs, and the second read is served by L2.
+// shard of it) is streamed twice by the same CTAs, and the second read is served on chip: by L2, or,
+// for unsplit rows of at most 48 KB, by shared memory (SMEM variant: one bulk TMA copy with an mbarrier
+// lands the row there and both passes read it from shared memory).
 //
 //   pass 1   128-bit loads with an L2 evict_last policy, online max / sum-exp -> (M, S, U, y_c)
 //   merge    CL > 1: the row is split over a thread-block cluster of CL CTAs (CTA r takes the r-th
