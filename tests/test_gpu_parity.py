@@ -490,3 +490,41 @@ def test_other_config_shapes_sampled_rows(cuda, name, rows):
     assert_dlogits_close(d[rows_idx], torch.from_numpy(an["dlogits"]), what=f"{name} sampled rows")
     zero = (mask == 0).nonzero()[:64, 0]
     assert (d[zero] == 0).all()
+
+
+def test_chunked_lm_head_and_loss(cuda):
+    """hidden @ W^T and the loss chunk by chunk: equals the oracle on the full logits, and the
+    chunk size does not change the result."""
+    from mllm_jax_b200.linear_loss import linear_grpo_value_and_grad
+
+    B, T, H, V = 6, 17, 64, 4096
+    g = torch.Generator().manual_seed(50)
+    hidden = (torch.randn(B, T, H, generator=g) * 0.5).to(torch.bfloat16).to(cuda)
+    weight = (torch.randn(V, H, generator=g) * 0.5).to(torch.bfloat16).to(cuda)
+    logits = torch.matmul(hidden, weight.t())  # what the chunks will hold
+    _, inputs = make_case(B, T + 1, V, seed=51, old="none")
+    ids, mask = inputs["input_ids"][:, 1:], inputs["labels"][:, 1:]
+    lg = logits.float().cpu()
+    lp0 = torch.log_softmax(lg, -1).gather(-1, ids.long()[..., None])[..., 0]
+    old = lp0 + 0.3 * torch.randn(B, T, generator=g)
+    nv = float(mask.sum())
+    # oracle on the shifted layout: append a dummy last row, prepend a dummy id / label
+    z = torch.zeros(B, 1, dtype=ids.dtype)
+    oin = {"input_ids": torch.cat([z, ids], 1), "labels": torch.cat([z, mask], 1), "advantages": inputs["advantages"],
+           "total_valid_token_count": nv, "old_per_token_logps": old}
+    ref = O.reference_value_and_grad(torch.cat([logits.cpu(), logits.cpu()[:, :1]], 1), oin)
+    dl = ref["dlogits"][:, :T].reshape(B * T, V)
+    dW_ref = dl.t() @ hidden.float().cpu().reshape(B * T, H)
+    dH_ref = (dl @ weight.float().cpu()).reshape(B, T, H)
+    outs = []
+    for chunk in (T, 3 * T, 10 ** 6):
+        out = linear_grpo_value_and_grad(hidden, weight, ids.to(cuda), mask.to(cuda), inputs["advantages"].to(cuda),
+                                         nv, old.to(cuda), chunk_rows=chunk)
+        torch.cuda.synchronize()
+        assert (out["per_token_logps"].cpu() - ref["per_token_logps"]).abs().max() <= LP_ATOL
+        assert_loss_close(out["loss"].item(), ref["loss"].item())
+        assert (out["dweight"].cpu() - dW_ref).abs().max() <= 2e-2 * dW_ref.abs().max()
+        assert (out["dhidden"].float().cpu() - dH_ref).abs().max() <= 2e-2 * dH_ref.abs().max()
+        outs.append(out)
+    assert torch.equal(outs[0]["per_token_logps"], outs[2]["per_token_logps"])
+    assert torch.equal(outs[0]["dhidden"], outs[2]["dhidden"])
