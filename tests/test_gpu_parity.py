@@ -232,7 +232,10 @@ def test_vocab_shards_on_one_gpu(cuda, k, softcap):
         assert torch.equal(p.loss, probs[0].loss)
 
 
-def test_golden_fixtures(cuda):
+@pytest.mark.parametrize("eager", [False, True])
+def test_golden_fixtures(cuda, eager):
+    """Committed fixtures through both autograd forms: separate forward / backward kernels, and the
+    eager form the module mirror uses (loss and gradient from one kernel)."""
     for f in sorted(os.listdir(GOLDEN)):
         if not f.endswith(".npz"):
             continue
@@ -245,7 +248,7 @@ def test_golden_fixtures(cuda):
         x = logits.clone().requires_grad_(True)
         out = G.grpo_token_loss(x, torch.from_numpy(z["input_ids"]).to(cuda), torch.from_numpy(z["labels"]).to(cuda),
                                 torch.from_numpy(z["advantages"]).to(cuda), float(z["total_valid_token_count"]),
-                                old, rf, **kw)
+                                old, rf, eager_grad=eager, **kw)
         out["loss"].backward()
         ref = {"loss": torch.tensor(float(z["loss"])), "per_token_logps": torch.from_numpy(z["per_token_logps"]),
                "token_entropy": torch.from_numpy(z["token_entropy"]), "dlogits": torch.from_numpy(z["dlogits"])}
