@@ -9,9 +9,8 @@
 //   loss_reduce_kernel: fixed-order sum of the per-token loss terms / total_valid.
 //   dlogits_kernel    : one CTA per logits row; second streaming pass writing
 //                       g*(softmax - onehot) in bf16; zero rows are write-only.
-#include <cstdlib>
-
-#include "grpo_cluster.cuh"
+//   scale_grad_kernel : applies a late cotangent to gradients written with cotangent 1
+//                       (returns at once when it is exactly 1).
 #include "grpo_common.cuh"
 #include "grpo_launch.h"
 #include "grpo_rowpass.cuh"
