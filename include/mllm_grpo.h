@@ -226,6 +226,40 @@ int mllm_grpo_fwd_static_scratch(const mllm_grpo_args* args, void* stream);
  * sample_entropy and sample_entropy_window. */
 int mllm_grpo_entropy_stats(const mllm_grpo_args* args, void* stream);
 
+/* Value-loss tail of the PPO actor-critic module (replaces plugins/training/ppo/module.py:104-140):
+ *   value_pred = values[:, :scored_rows]                                        (:104)
+ *   returns    = given, else advantages + value_pred (and then moves with the values)   (:105-107)
+ *   old_values = given, else the values themselves without gradient             (:116-118)
+ *   term       = max((v - r)^2, (old + clip(v - old, -c, c) - r)^2), or (v - r)^2 without a range  (:131-136)
+ *   value_loss = sum(term * mask) / total_valid_token_count                     (:138)
+ * out[0] = value_loss, out[1] = mean(value_pred), out[2] = mean(returns) (:147-148, plain means over
+ * all n_seqs x scored_rows positions).  dvalues = grad_scale x d value_loss / d values, zero at
+ * positions >= scored_rows; pass grad_scale = value_coef x the cotangent of the total loss (:140).
+ * All arrays are f32 in device memory; returns, old_values and mask are [n_seqs, scored_rows]
+ * row-major, values and dvalues [n_seqs, seq_rows].  Sums are taken in double precision in a
+ * fixed order.  Asynchronous on the stream, allocates nothing. */
+typedef struct mllm_ppo_value_args {
+  uint64_t struct_size; /* sizeof(mllm_ppo_value_args) */
+  int64_t n_seqs;
+  int64_t seq_rows;    /* L */
+  int64_t scored_rows; /* L - 1 in the reference */
+  float clip_range;    /* value_clip_range (:20); negative = None */
+  float grad_scale;
+  float total_valid;   /* total_valid_token_count, used when total_valid_dev is NULL */
+  int32_t adv_per_token; /* advantages are [n_seqs, scored_rows] instead of [n_seqs] */
+  const float* total_valid_dev; /* optional scalar in device memory */
+  const float* values;
+  const float* returns;    /* optional */
+  const float* advantages; /* required when returns is NULL */
+  const float* old_values; /* optional */
+  const float* mask;       /* optional: NULL = every position counts */
+  float* dvalues;          /* optional */
+  float* out;              /* [3] */
+  double* workspace;       /* mllm_ppo_value_workspace_bytes(n_seqs, seq_rows) bytes, 8-byte aligned */
+} mllm_ppo_value_args;
+int mllm_ppo_value_loss(const mllm_ppo_value_args* args, void* stream);
+int64_t mllm_ppo_value_workspace_bytes(int64_t n_seqs, int64_t seq_rows);
+
 /* Bytes of loss_terms scratch a problem of n_tokens = B*T needs. */
 int64_t mllm_grpo_workspace_bytes(int64_t n_tokens);
 

@@ -20,7 +20,7 @@ EXPORTS = (
     "mllm_grpo_logprobs", "mllm_grpo_workspace_bytes", "mllm_grpo_abi_version", "mllm_grpo_status_string",
     "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count", "mllm_grpo_fwd_static_scratch",
     "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_exchange_bytes", "mllm_grpo_enable_peer_access",
-    "mllm_grpo_entropy_stats", "mllm_grpo_scale_grad",
+    "mllm_grpo_entropy_stats", "mllm_grpo_scale_grad", "mllm_ppo_value_loss", "mllm_ppo_value_workspace_bytes",
 )
 
 
@@ -45,6 +45,19 @@ class GrpoArgs(C.Structure):
         ("device_status", C.c_void_p),
         ("peer_exchange", C.c_void_p * 8), ("exchange_epoch", C.c_int32), ("reserved1", C.c_int32),
         ("sample_entropy", C.c_void_p), ("sample_entropy_window", C.c_void_p),
+    ]
+
+
+class PpoValueArgs(C.Structure):
+    """Mirror of `struct mllm_ppo_value_args`."""
+
+    _fields_ = [
+        ("struct_size", C.c_uint64),
+        ("n_seqs", C.c_int64), ("seq_rows", C.c_int64), ("scored_rows", C.c_int64),
+        ("clip_range", C.c_float), ("grad_scale", C.c_float), ("total_valid", C.c_float), ("adv_per_token", C.c_int32),
+        ("total_valid_dev", C.c_void_p),
+        ("values", C.c_void_p), ("returns", C.c_void_p), ("advantages", C.c_void_p), ("old_values", C.c_void_p),
+        ("mask", C.c_void_p), ("dvalues", C.c_void_p), ("out", C.c_void_p), ("workspace", C.c_void_p),
     ]
 
 
@@ -75,6 +88,10 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(GrpoArgs), C.c_void_p]
         fn.restype = C.c_int
+    lib.mllm_ppo_value_loss.argtypes = [C.POINTER(PpoValueArgs), C.c_void_p]
+    lib.mllm_ppo_value_loss.restype = C.c_int
+    lib.mllm_ppo_value_workspace_bytes.argtypes = [C.c_int64, C.c_int64]
+    lib.mllm_ppo_value_workspace_bytes.restype = C.c_int64
     lib.mllm_grpo_workspace_bytes.argtypes = [C.c_int64]
     lib.mllm_grpo_workspace_bytes.restype = C.c_int64
     lib.mllm_grpo_enable_peer_access.argtypes = [C.c_int]
@@ -90,10 +107,10 @@ def load():
     return lib
 
 
-def call(name: str, args: GrpoArgs, stream: int) -> None:
+def call(name: str, args, stream: int) -> None:
     """Invoke one launcher; raise GrpoError on a non-zero status."""
     lib = load()
-    args.struct_size = C.sizeof(GrpoArgs)
+    args.struct_size = C.sizeof(type(args))
     status = getattr(lib, name)(C.byref(args), C.c_void_p(stream))
     if status != 0:
         raise GrpoError(name, status, lib.mllm_grpo_status_string(status).decode(),

@@ -19,6 +19,8 @@ static int fail_cuda(cudaError_t e) {
   return MLLM_GRPO_ERR_LAUNCH;
 }
 
+int record_cuda_error(cudaError_t e) { return fail_cuda(e); }
+
 // What an entry point needs from the argument struct.
 enum Need : unsigned {
   kLogits = 1u << 0,

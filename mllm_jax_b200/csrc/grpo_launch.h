@@ -10,6 +10,8 @@ namespace grpo {
 
 // Bumps the process-wide count of kernels launched by this library.
 void count_launch();
+// Stores the error's text for mllm_grpo_last_cuda_error() and returns MLLM_GRPO_ERR_LAUNCH.
+int record_cuda_error(cudaError_t e);
 
 // mode: 0 full forward, 1 shard partials, 2 log-probs only.  ent: 0 none, 1 temperature == 1, 2 otherwise.
 cudaError_t launch_row_stats(const KernelParams& p, int mode, int ent, cudaStream_t s);

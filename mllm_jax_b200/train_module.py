@@ -2,7 +2,8 @@
 
 `TrainGRPOModule` keeps the fields, the `inputs` dict and the returned dict of
 MLLM_JAX/train_modules/__init__.py:84-192; `ppo_policy_terms` covers the policy
-part of PPOActorCriticModule.__call__ (plugins/training/ppo/module.py:66-102).
+part of PPOActorCriticModule.__call__ (plugins/training/ppo/module.py:66-102) and
+`ppo_value_loss` its value-loss tail (:104-140).
 The model is any callable `model(input_ids=..., attention_mask=...) ->
 (logits, cache)` producing bf16 CUDA logits; gradients flow into it through
 torch autograd exactly where jax.value_and_grad differentiates the reference.
@@ -114,8 +115,8 @@ def ppo_policy_terms(logits: torch.Tensor, inputs: Mapping[str, Any], *, tempera
                      epsilon_low: float = 0.2, epsilon_high: float = 0.2) -> dict:
     """Policy loss, global entropy and log-probs as PPOActorCriticModule computes them
     (plugins/training/ppo/module.py:66-102): advantages [B], [B, 1] or [B, L-1]; entropy is one
-    masked mean over the batch with a 1e-8 guard (:77).  The value-loss tail (:104-140) is a
-    [B, L] elementwise computation on the value head and stays with the caller."""
+    masked mean over the batch with a 1e-8 guard (:77).  The value-loss tail (:104-140) is
+    `ppo_value_loss`."""
     labels = inputs["labels"]
     out = grpo_token_loss(
         logits, inputs["input_ids"], labels, inputs["advantages"],
@@ -126,3 +127,75 @@ def ppo_policy_terms(logits: torch.Tensor, inputs: Mapping[str, Any], *, tempera
     m = labels[:, 1:].to(torch.float32)
     entropy = (out["token_entropy"] * m).sum() / (m.sum() + 1e-8)
     return {"policy_loss": out["loss"], "entropy": entropy, "per_token_logps": out["per_token_logps"].detach()}
+
+
+def _to_positions(x: torch.Tensor, name: str, shape: tuple, dev) -> torch.Tensor:
+    """[B], [B, 1] or [B, T] -> contiguous f32 [B, T] (the broadcasting of ppo/module.py:108-125)."""
+    x = x.to(device=dev, dtype=torch.float32)
+    if x.dim() == 1:
+        x = x[:, None]
+    if tuple(x.shape) != shape:
+        if x.shape[1] == 1:
+            x = x.expand(shape)
+        else:
+            raise ValueError(f"{name} shape {tuple(x.shape)} does not match value_pred {shape}")
+    return x.contiguous()
+
+
+def ppo_value_loss(values: torch.Tensor, inputs: Mapping[str, Any], *, value_clip_range: Optional[float] = 0.2,
+                   value_coef: float = 0.5, grad_scale: float = 1.0) -> dict:
+    """Value-loss tail of PPOActorCriticModule.__call__ (plugins/training/ppo/module.py:104-140)
+    through mllm_ppo_value_loss.
+
+    values [B, L] is the value head's output for every position; `inputs` holds labels [B, L],
+    advantages, and optionally returns, old_values (or values), total_valid_token_count, with the
+    reference's meanings and broadcasting.  Returns value_loss, value_pred_mean, return_mean
+    (scalars) and dvalues [B, L] = grad_scale x value_coef x d value_loss / d values, which is the
+    value head's share of the gradient of loss = policy_loss + value_coef x value_loss (:140)."""
+    from . import _lib
+
+    if values.dim() != 2 or values.shape[1] < 2:
+        raise ValueError(f"values must be [B, L] with L >= 2, got {tuple(values.shape)}")
+    if not values.is_cuda:
+        raise RuntimeError("ppo_value_loss needs CUDA tensors: the kernels have no CPU path")
+    dev = values.device
+    B, L = values.shape
+    T = L - 1
+    shape = (B, T)
+    v = values.detach().to(torch.float32).contiguous()
+    mask = inputs["labels"][:, 1:].to(device=dev, dtype=torch.float32).contiguous()      # :67
+    returns = inputs.get("returns")
+    adv = None
+    if returns is None:
+        adv = _to_positions(inputs["advantages"], "advantages", shape, dev)              # :87-94, :107
+    else:
+        returns = _to_positions(returns, "returns", shape, dev)                          # :108-114
+    old = inputs.get("old_values", inputs.get("values"))                                 # :116
+    if old is not None:
+        old = _to_positions(old, "old_values", shape, dev)                               # :119-125
+    tv = inputs.get("total_valid_token_count")
+    tv_dev = None
+    if tv is None:
+        tv_dev = mask.sum().reshape(1)                                                   # :101
+    elif isinstance(tv, torch.Tensor):
+        tv_dev = tv.to(device=dev, dtype=torch.float32).reshape(1)
+    out = torch.empty(3, dtype=torch.float32, device=dev)
+    dvalues = torch.empty(B, L, dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    work = torch.empty(int(lib.mllm_ppo_value_workspace_bytes(B, L)) // 8, dtype=torch.float64, device=dev)
+    a = _lib.PpoValueArgs()
+    a.n_seqs, a.seq_rows, a.scored_rows = B, L, T
+    a.clip_range = -1.0 if value_clip_range is None else float(value_clip_range)
+    a.grad_scale = float(grad_scale) * float(value_coef)
+    a.total_valid = float("nan") if tv_dev is not None else float(tv)
+    a.adv_per_token = 1
+    a.total_valid_dev = None if tv_dev is None else tv_dev.data_ptr()
+    a.values = v.data_ptr()
+    a.returns = None if returns is None else returns.data_ptr()
+    a.advantages = None if adv is None else adv.data_ptr()
+    a.old_values = None if old is None else old.data_ptr()
+    a.mask = mask.data_ptr()
+    a.dvalues, a.out, a.workspace = dvalues.data_ptr(), out.data_ptr(), work.data_ptr()
+    with torch.cuda.device(dev):
+        _lib.call("mllm_ppo_value_loss", a, torch.cuda.current_stream().cuda_stream)
+    return {"value_loss": out[0], "value_pred_mean": out[1], "return_mean": out[2], "dvalues": dvalues}

@@ -157,6 +157,46 @@ def ppo_policy_call(logits: torch.Tensor, inputs: Mapping[str, Any], *, temperat
     return {"policy_loss": policy_loss, "entropy": entropy.detach(), "per_token_logps": per_token_logps.detach()}
 
 
+def ppo_value_call(values: torch.Tensor, inputs: Mapping[str, Any], *, value_clip_range: Optional[float] = 0.2,
+                   dtype=torch.float32) -> dict:
+    """Value-loss tail of PPOActorCriticModule.__call__ (plugins/training/ppo/module.py:104-148).
+    `values` [B, L] may require grad; autograd then gives d value_loss / d values."""
+    mask_loss = inputs["labels"][:, 1:].to(dtype)                             # :67
+    value_pred = values[:, :-1]                                               # :104
+    shape = value_pred.shape
+
+    def positions(x, name):
+        if x.dim() == 1:
+            x = x[:, None]
+        if x.shape != shape:
+            if x.shape[1] == 1:
+                x = x.expand(shape)
+            else:
+                raise ValueError(f"{name} shape {tuple(x.shape)} does not match value_pred {tuple(shape)}")
+        return x
+
+    returns = inputs.get("returns")                                           # :105
+    if returns is None:
+        returns = positions(inputs["advantages"].to(dtype), "advantages") + value_pred          # :106-107
+    returns = positions(returns, "returns")                                   # :108-114
+    old_values = inputs.get("old_values", inputs.get("values"))               # :116
+    if old_values is None:
+        old_values = value_pred.detach()                                      # :117-118
+    old_values = positions(old_values, "old_values")                          # :119-125
+    value_pred, returns, old_values = value_pred.to(dtype), returns.to(dtype), old_values.to(dtype)  # :127-129
+    if value_clip_range is not None:
+        c = float(value_clip_range)
+        value_clipped = old_values + torch.clamp(value_pred - old_values, -c, c)                # :133
+        value_loss = torch.maximum((value_pred - returns) ** 2, (value_clipped - returns) ** 2)  # :134
+    else:
+        value_loss = (value_pred - returns) ** 2                              # :136
+    tv = inputs.get("total_valid_token_count")
+    total_valid_token_count = mask_loss.sum() if tv is None else tv           # :101
+    value_loss = (value_loss * mask_loss).sum() / total_valid_token_count     # :138
+    return {"value_loss": value_loss, "value_pred_mean": value_pred.mean().detach(),            # :147
+            "return_mean": returns.mean().detach()}                           # :148
+
+
 def sft_call(logits: torch.Tensor, inputs: Mapping[str, Any], *, label_ignore_id: int = -100,
              dtype=torch.float32) -> dict:
     """TrainSftModule.__call__ from the logits on (plugins/sft/jax/sft_module.py:29-45)."""

@@ -17,7 +17,7 @@ HEADER = os.path.join(ROOT, "include", "mllm_grpo.h")
 def _declared_functions():
     text = open(HEADER).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(mllm_grpo_[a-z_0-9]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(mllm_(?:grpo|ppo)_[a-z_0-9]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol(built_lib):
@@ -46,6 +46,34 @@ def test_ctypes_struct_matches_c_layout(tmp_path):
     assert int(out[0]) == C.sizeof(_lib.GrpoArgs)
     for f, off in zip(fields, out[1:]):
         assert getattr(_lib.GrpoArgs, f).offset == int(off), f
+
+
+def test_value_struct_matches_c_layout(tmp_path):
+    fields = [f[0] for f in _lib.PpoValueArgs._fields_]
+    src = tmp_path / "layout.c"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "mllm_grpo.h"', "int main(void){",
+             'printf("%zu\\n", sizeof(mllm_ppo_value_args));']
+    lines += [f'printf("%zu\\n", offsetof(mllm_ppo_value_args, {f}));' for f in fields]
+    lines += ["return 0;}"]
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", f"-I{os.path.join(ROOT, 'include')}", str(src), "-o",
+                    str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert int(out[0]) == C.sizeof(_lib.PpoValueArgs)
+    for f, off in zip(fields, out[1:]):
+        assert getattr(_lib.PpoValueArgs, f).offset == int(off), f
+
+
+def test_value_loss_validation(built_lib):
+    a = _lib.PpoValueArgs()
+    lib = _lib.load()
+    assert lib.mllm_ppo_value_loss(C.byref(a), None) == 4  # struct size
+    a.struct_size = C.sizeof(_lib.PpoValueArgs)
+    assert lib.mllm_ppo_value_loss(C.byref(a), None) == 2  # shape
+    a.n_seqs, a.seq_rows, a.scored_rows = 2, 4, 3
+    assert lib.mllm_ppo_value_loss(C.byref(a), None) == 1  # null pointers
+    assert lib.mllm_ppo_value_workspace_bytes(2, 4) == 24 and lib.mllm_ppo_value_workspace_bytes(0, 4) == 0
 
 
 def _valid_args():

@@ -531,3 +531,36 @@ def test_chunked_lm_head_and_loss(cuda):
         outs.append(out)
     assert torch.equal(outs[0]["per_token_logps"], outs[2]["per_token_logps"])
     assert torch.equal(outs[0]["dhidden"], outs[2]["dhidden"])
+
+
+@pytest.mark.parametrize("clip", [0.2, None])
+@pytest.mark.parametrize("returns", ["given", "per_sample", "absent"])
+@pytest.mark.parametrize("old", ["given", "absent"])
+def test_ppo_value_loss(cuda, clip, returns, old):
+    """Value-loss tail of the PPO module: loss, monitors and the gradient with respect to the values."""
+    B, L = 5, 301
+    g = torch.Generator().manual_seed(61)
+    values = torch.randn(B, L, generator=g)
+    labels = (torch.rand(B, L, generator=g) < 0.6).float()
+    inputs = {"labels": labels, "advantages": torch.randn(B, generator=g)}
+    if returns == "given":
+        inputs["returns"] = values[:, :-1] + torch.randn(B, L - 1, generator=g)
+    elif returns == "per_sample":
+        inputs["returns"] = torch.randn(B, 1, generator=g)
+    if old == "given":
+        inputs["old_values"] = values[:, :-1] + 0.3 * torch.randn(B, L - 1, generator=g)
+    for tv in (None, 777.0):
+        if tv is not None:
+            inputs["total_valid_token_count"] = tv
+        v = values.clone().requires_grad_(True)
+        ref = O.ppo_value_call(v, inputs, value_clip_range=clip)
+        (0.5 * ref["value_loss"]).backward()
+        out = G.ppo_value_loss(values.to(cuda), to_device(inputs, cuda), value_clip_range=clip, value_coef=0.5)
+        torch.cuda.synchronize()
+        for key in ("value_loss", "value_pred_mean", "return_mean"):
+            assert out[key].item() == pytest.approx(ref[key].item(), rel=1e-5, abs=1e-6), key
+        dref = v.grad
+        assert (out["dvalues"].cpu() - dref).abs().max() <= 1e-5 * dref.abs().max() + 1e-9
+        assert (out["dvalues"][:, -1] == 0).all()
+    with pytest.raises(ValueError):
+        G.ppo_value_loss(values.to(cuda), {**to_device(inputs, cuda), "returns": torch.zeros(B, 4)})

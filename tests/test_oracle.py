@@ -259,3 +259,53 @@ def test_sft_cross_entropy_known_answer():
     assert abs(out["loss"].item() - math.log(V)) < 1e-5 and int(out["token_count"]) == B * (L - 2)
     empty = O.sft_call(logits, {"labels": torch.full((B, L), -100), "attention_mask": att})
     assert empty["loss"].item() == 0.0
+
+
+def _value_case(B=3, L=9, seed=60):
+    g = torch.Generator().manual_seed(seed)
+    values = torch.randn(B, L, generator=g)
+    labels = (torch.rand(B, L, generator=g) < 0.7).float()
+    labels[0, 1:] = 1.0
+    return values, {"labels": labels, "advantages": torch.randn(B, generator=g),
+                    "returns": torch.randn(B, L - 1, generator=g),
+                    "old_values": values[:, :-1] + 0.3 * torch.randn(B, L - 1, generator=g)}
+
+
+def test_value_loss_known_answers():
+    """Hand-computed cases of the value-loss tail (plugins/training/ppo/module.py:104-138)."""
+    labels = torch.ones(1, 4)
+    values = torch.tensor([[1.0, 2.0, 3.0, 99.0]])
+    base = {"labels": labels, "advantages": torch.zeros(1)}
+    # no range: plain squared error over positions 0..L-2
+    out = O.ppo_value_call(values, {**base, "returns": torch.tensor([[0.0, 0.0, 0.0]])}, value_clip_range=None)
+    assert out["value_loss"].item() == pytest.approx((1 + 4 + 9) / 3)
+    assert out["value_pred_mean"].item() == pytest.approx(2.0) and out["return_mean"].item() == 0.0
+    # range 0.5 around old = 0: clipped prediction 0.5, (0.5 - r)^2 with r = 4 is the larger term at every position
+    out = O.ppo_value_call(values, {**base, "returns": torch.full((1, 3), 4.0), "old_values": torch.zeros(1, 3)},
+                           value_clip_range=0.5)
+    assert out["value_loss"].item() == pytest.approx(3.5 ** 2)
+    # returns absent: advantages + value_pred, so both terms are advantages^2 when old_values is absent as well
+    out = O.ppo_value_call(values, {"labels": labels, "advantages": torch.tensor([3.0])})
+    assert out["value_loss"].item() == pytest.approx(9.0)
+    assert out["return_mean"].item() == pytest.approx(5.0)
+    # mask and the global normaliser
+    lab = torch.tensor([[1.0, 1.0, 0.0, 1.0]])
+    out = O.ppo_value_call(values, {"labels": lab, "advantages": torch.zeros(1), "returns": torch.zeros(1, 3),
+                                    "total_valid_token_count": 10.0}, value_clip_range=None)
+    assert out["value_loss"].item() == pytest.approx((1 + 9) / 10.0)  # position t is weighted by labels[t + 1]
+
+
+def test_value_loss_gradient_cases():
+    """d value_loss / d values: 2(v - r) m / Nv where the unclipped term is active, 0 where the clipped one is."""
+    values = torch.tensor([[1.0, 1.0, 1.0, 7.0]], requires_grad=True)
+    inputs = {"labels": torch.ones(1, 4), "advantages": torch.zeros(1),
+              "returns": torch.tensor([[3.0, 3.0, 0.0]]),
+              # position 0: inside the range; 1: clipped to 0.5 and (0.5 - 3)^2 is larger -> zero gradient;
+              # 2: clipped to 0.5 but (1 - 0)^2 > (0.5 - 0)^2 -> the unclipped term drives the gradient
+              "old_values": torch.tensor([[1.0, 0.0, 0.0]])}
+    O.ppo_value_call(values, inputs, value_clip_range=0.5)["value_loss"].backward()
+    g = values.grad[0]
+    assert g[0].item() == pytest.approx(2 * (1 - 3) / 3)
+    assert g[1].item() == 0.0
+    assert g[2].item() == pytest.approx(2 * (1 - 0) / 3)
+    assert g[3].item() == 0.0  # the last position never enters (values[:, :-1])
