@@ -14,11 +14,17 @@ from .ops import (  # noqa: F401
     token_logprobs,
 )
 from .linear_loss import linear_grpo_value_and_grad  # noqa: F401
-from .train_module import TrainGRPOModule, per_sample_entropy, ppo_policy_terms, ppo_value_loss  # noqa: F401
+from .train_module import (  # noqa: F401
+    TrainGRPOModule,
+    per_sample_entropy,
+    ppo_actor_critic_terms,
+    ppo_policy_terms,
+    ppo_value_loss,
+)
 
 __all__ = [
     "GrpoError", "LIB_PATH", "LossConfig", "TokenLossProblem", "TrainGRPOModule", "grpo_token_loss",
-    "grpo_token_loss_flat", "grpo_value_and_grad", "linear_grpo_value_and_grad", "launch_count", "per_sample_entropy", "ppo_policy_terms", "ppo_value_loss",
+    "grpo_token_loss_flat", "grpo_value_and_grad", "linear_grpo_value_and_grad", "launch_count", "per_sample_entropy", "ppo_actor_critic_terms", "ppo_policy_terms", "ppo_value_loss",
     "sft_cross_entropy",
     "token_logprobs",
 ]

@@ -199,3 +199,40 @@ def ppo_value_loss(values: torch.Tensor, inputs: Mapping[str, Any], *, value_cli
     with torch.cuda.device(dev):
         _lib.call("mllm_ppo_value_loss", a, torch.cuda.current_stream().cuda_stream)
     return {"value_loss": out[0], "value_pred_mean": out[1], "return_mean": out[2], "dvalues": dvalues}
+
+
+class _ValueLoss(torch.autograd.Function):
+    """value_loss as a differentiable function of the value head's output (the kernel has already
+    produced d value_loss / d values in the forward, as in the eager form of the token loss)."""
+
+    @staticmethod
+    def forward(ctx, values, inputs, value_clip_range):
+        out = ppo_value_loss(values, inputs, value_clip_range=value_clip_range, value_coef=1.0)
+        ctx.save_for_backward(out["dvalues"])
+        ctx.values_dtype = values.dtype
+        ctx.mark_non_differentiable(out["value_pred_mean"], out["return_mean"])
+        return out["value_loss"], out["value_pred_mean"], out["return_mean"]
+
+    @staticmethod
+    def backward(ctx, grad_loss, _grad_mean, _grad_return):
+        (dvalues,) = ctx.saved_tensors
+        return (grad_loss * dvalues).to(ctx.values_dtype), None, None
+
+
+def ppo_actor_critic_terms(logits: torch.Tensor, values: torch.Tensor, inputs: Mapping[str, Any], *,
+                           temperature: float = 1.0, epsilon_low: float = 0.2, epsilon_high: float = 0.2,
+                           value_coef: float = 0.5, value_clip_range: Optional[float] = 0.2,
+                           entropy_coef: float = 0.0) -> dict:
+    """The return dict of PPOActorCriticModule.__call__ (plugins/training/ppo/module.py:142-150) from
+    the lm_head's logits [B, L, V] and the value head's values [B, L]; `loss` is differentiable with
+    respect to both.  A non-zero entropy_coef (:140; 0.0 in every configuration the reference ships)
+    needs the gradient of the entropy with respect to the logits, which the kernels do not produce."""
+    if float(entropy_coef) != 0.0:
+        raise NotImplementedError("entropy_coef != 0 needs d entropy / d logits, which is not implemented")
+    pol = ppo_policy_terms(logits, inputs, temperature=temperature, epsilon_low=epsilon_low,
+                           epsilon_high=epsilon_high)
+    value_loss, value_pred_mean, return_mean = _ValueLoss.apply(values, inputs, value_clip_range)
+    loss = pol["policy_loss"] + float(value_coef) * value_loss                                     # :140
+    return {"loss": loss, "policy_loss": pol["policy_loss"], "value_loss": value_loss, "entropy": pol["entropy"],
+            "value_pred_mean": value_pred_mean, "return_mean": return_mean,
+            "per_token_logps": pol["per_token_logps"]}

@@ -564,3 +564,29 @@ def test_ppo_value_loss(cuda, clip, returns, old):
         assert (out["dvalues"][:, -1] == 0).all()
     with pytest.raises(ValueError):
         G.ppo_value_loss(values.to(cuda), {**to_device(inputs, cuda), "returns": torch.zeros(B, 4)})
+
+
+def test_ppo_actor_critic_terms(cuda):
+    """Return dict of the PPO module: total loss and its gradient into the value head and the logits."""
+    logits, inputs = make_case(3, 40, 700, seed=62, old="wide", per_token_adv=True)
+    g = torch.Generator().manual_seed(63)
+    values = torch.randn(3, 40, generator=g)
+    inputs = {**inputs, "returns": torch.randn(3, 39, generator=g), "old_values": values[:, :-1] + 0.25}
+    v = values.clone().requires_grad_(True)
+    ref_p = O.ppo_policy_call(logits, inputs)
+    ref_v = O.ppo_value_call(v, inputs, value_clip_range=0.2)
+    ref_loss = ref_p["policy_loss"] + 0.5 * ref_v["value_loss"]
+    ref_loss.backward()
+    x = logits.to(cuda).requires_grad_(True)
+    vg = values.to(cuda).requires_grad_(True)
+    out = G.ppo_actor_critic_terms(x, vg, to_device(inputs, cuda))
+    out["loss"].backward()
+    torch.cuda.synchronize()
+    assert_loss_close(out["loss"].item(), ref_loss.item())
+    assert_loss_close(out["value_loss"].item(), ref_v["value_loss"].item())
+    assert (vg.grad.cpu() - v.grad).abs().max() <= 1e-5 * v.grad.abs().max()
+    assert x.grad is not None and x.grad.abs().max() > 0
+    assert sorted(out) == sorted(["loss", "policy_loss", "value_loss", "entropy", "value_pred_mean", "return_mean",
+                                  "per_token_logps"])
+    with pytest.raises(NotImplementedError):
+        G.ppo_actor_critic_terms(x, vg, to_device(inputs, cuda), entropy_coef=0.01)
