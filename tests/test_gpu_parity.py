@@ -459,12 +459,13 @@ def test_extreme_logits_and_tiny_vocab(cuda):
     assert torch.equal(torch.isfinite(out["per_token_logps"].cpu()), finite)
     assert (out["per_token_logps"].cpu()[finite] - ref["per_token_logps"][finite]).abs().max() <= LP_ATOL
     # one column: log-prob 0, entropy 0, zero gradient
-    one = torch.randn(2, 4, 1).to(torch.bfloat16)
+    one = torch.randn(2, 4, 1, generator=torch.Generator().manual_seed(64)).to(torch.bfloat16)
     ids = torch.zeros(2, 4, dtype=torch.int32)
     o1 = G.grpo_value_and_grad(one.to(cuda), ids.to(cuda), torch.ones(2, 4, dtype=torch.int32).to(cuda),
                                torch.tensor([1.0, -1.0]).to(cuda), 6.0, shifted=True)
     assert o1["per_token_logps"].abs().max() == 0 and o1["token_entropy"].abs().max() == 0
-    assert (o1["dlogits"] == 0).all() and o1["loss"].item() == 0.0
+    # g*(softmax - onehot) with softmax == 1: zero up to the f32 rounding of g*e^(x - lse) against g (|g| <= 1/6)
+    assert o1["dlogits"].float().abs().max() <= 1e-6 and o1["loss"].item() == 0.0
 
 
 @pytest.mark.parametrize("name,rows", [("cfg2", 4), ("cfg3", 2)])

@@ -252,23 +252,13 @@ def test_sft_cross_entropy_known_answer():
     """Uniform logits: every supervised token costs log V; unsupervised ones are ignored."""
     B, L, V = 2, 6, 50
     logits = torch.zeros(B, L, V, dtype=torch.bfloat16)
-    labels = torch.randint(0, V, (B, L))
+    labels = torch.randint(0, V, (B, L), generator=torch.Generator().manual_seed(59))
     labels[:, :2] = -100
     att = torch.ones(B, L, dtype=torch.int32)
     out = O.sft_call(logits, {"labels": labels, "attention_mask": att})
     assert abs(out["loss"].item() - math.log(V)) < 1e-5 and int(out["token_count"]) == B * (L - 2)
     empty = O.sft_call(logits, {"labels": torch.full((B, L), -100), "attention_mask": att})
     assert empty["loss"].item() == 0.0
-
-
-def _value_case(B=3, L=9, seed=60):
-    g = torch.Generator().manual_seed(seed)
-    values = torch.randn(B, L, generator=g)
-    labels = (torch.rand(B, L, generator=g) < 0.7).float()
-    labels[0, 1:] = 1.0
-    return values, {"labels": labels, "advantages": torch.randn(B, generator=g),
-                    "returns": torch.randn(B, L - 1, generator=g),
-                    "old_values": values[:, :-1] + 0.3 * torch.randn(B, L - 1, generator=g)}
 
 
 def test_value_loss_known_answers():
