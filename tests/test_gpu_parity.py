@@ -591,3 +591,33 @@ def test_ppo_actor_critic_terms(cuda):
                                   "per_token_logps"])
     with pytest.raises(NotImplementedError):
         G.ppo_actor_critic_terms(x, vg, to_device(inputs, cuda), entropy_coef=0.01)
+
+
+@pytest.mark.parametrize("V", [18992, 50000, 151936])
+def test_cuda_graph_capture_and_replay(cuda, V):
+    """The entry points enqueue on the caller's stream, allocate nothing and never synchronise, so a
+    step can be captured in a CUDA graph; replays reproduce the eager launch bit for bit (staged
+    short rows, register-fed rows and the cluster split of long rows)."""
+    logits, inputs = make_case(2, 9, V, seed=70, old="wide", ref=True)
+    din = to_device(inputs, cuda)
+    out = G.grpo_value_and_grad(logits.to(cuda), din["input_ids"], din["labels"], din["advantages"],
+                                din["total_valid_token_count"], din["old_per_token_logps"],
+                                din["ref_per_token_logps"], shifted=True, cfg=G.LossConfig(beta=0.04))
+    prob = out["problem"]
+    torch.cuda.synchronize()
+    want = [t.clone() for t in (prob.dlogits, prob.loss, prob.per_token_logps, prob.token_entropy)]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        prob.run("mllm_grpo_fwd_bwd", reuse_args=True)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        prob.run("mllm_grpo_fwd_bwd", reuse_args=True)
+    for _ in range(2):
+        for t in (prob.dlogits, prob.loss, prob.per_token_logps, prob.token_entropy):
+            t.fill_(7.0)
+        graph.replay()
+        torch.cuda.synchronize()
+        for got, ref in zip((prob.dlogits, prob.loss, prob.per_token_logps, prob.token_entropy), want):
+            assert torch.equal(got, ref)
