@@ -257,40 +257,53 @@ cudaError_t launch_e(const KernelParams& p, int ent, bool smem, cudaStream_t s) 
 }
 
 template <int CL, bool SHARDED>
-cudaError_t launch_t(const KernelParams& p, int ent, int threads, bool smem, cudaStream_t s) {
+cudaError_t launch_t(const KernelParams& p, int ent, int threads, int unroll, bool smem, cudaStream_t s) {
   if (threads <= 64 && CL == 1) return launch_e<1, 64, 8, SHARDED>(p, ent, smem, s);
+  if constexpr (CL >= 2 && !SHARDED) {  // batch sizes other than 8 exist for cluster slices only
+    if (threads <= 128 && unroll == 6) return launch_e<CL, 128, 6, SHARDED>(p, ent, smem, s);
+    if (threads <= 128 && unroll == 10) return launch_e<CL, 128, 10, SHARDED>(p, ent, smem, s);
+  }
   if (threads <= 128) return launch_e<CL, 128, 8, SHARDED>(p, ent, smem, s);
   if (threads <= 256 || CL > 1) return launch_e<CL, 256, 4, SHARDED>(p, ent, smem, s);
   return launch_e<CL, 512, 4, SHARDED>(p, ent, smem, s);
 }
 
 template <bool SHARDED>
-cudaError_t launch_c(const KernelParams& p, int ent, int cluster, int threads, bool smem, cudaStream_t s) {
+cudaError_t launch_c(const KernelParams& p, int ent, int cluster, int threads, int unroll, bool smem, cudaStream_t s) {
   switch (cluster) {
-    case 1: return launch_t<1, SHARDED>(p, ent, threads, smem, s);
-    case 2: return launch_t<2, SHARDED>(p, ent, threads, smem, s);
-    case 4: return launch_t<4, SHARDED>(p, ent, threads, smem, s);
-    default: return launch_t<8, SHARDED>(p, ent, threads, smem, s);
+    case 1: return launch_t<1, SHARDED>(p, ent, threads, unroll, smem, s);
+    case 2: return launch_t<2, SHARDED>(p, ent, threads, unroll, smem, s);
+    case 4: return launch_t<4, SHARDED>(p, ent, threads, unroll, smem, s);
+    default: return launch_t<8, SHARDED>(p, ent, threads, unroll, smem, s);
   }
 }
 
 }  // namespace
 
-// Cluster size and thread count for a row of `vocab` columns: slices of roughly 32-48 KB.
-void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, int* threads, bool* smem) {
+// Cluster size, thread count and load-batch size for a row of `vocab` columns: slices of roughly 32-48 KB.
+void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, int* threads, bool* smem, int* unroll) {
   const int64_t row_bytes = p.vocab * 2;
   int cl = row_bytes >= 96 * 1024 ? 4 : (row_bytes >= 56 * 1024 ? 2 : 1);
-  if (row_bytes >= 192 * 1024) {
-    // 8 or 4 CTAs per row: take the split whose per-thread vector count leaves the smaller share to
-    // the one-vector-at-a-time remainder loop (128 threads, batches of 8).  Measured on one B200:
-    // V=151936 -> 8 (3.45 vs 3.54 ms), V=128256 -> 4 (12.4 vs 14.1 ms), V=256000 -> 4 (16.0 vs 16.6 ms).
+  int un = 8;
+  if (cl > 1) {
+    // A thread of a 128-thread CTA loads its slice in batches of `un` 16-byte vectors and finishes with a
+    // one-vector-at-a-time remainder loop, which has little memory parallelism.  Take the split (8 or 4 CTAs
+    // for rows of 192 KB and more) and the batch size that leave the smallest share to that loop; the soft-cap
+    // kernels need too many registers for batches of 10.  Measured on one B200, batch 8 -> chosen:
+    // V=151936: 3.49 -> 3.44 ms (8 CTAs, batches of 6); V=128256: 12.34 -> 11.60 ms (4 CTAs, batches of 10);
+    // V=256000 with soft-cap: 15.99 -> 15.11 ms (batches of 6; 8 and 4 CTAs alike).
+    const bool cap = p.softcap > 0.f;
     double best = 2.0;
-    for (int c = 8; c >= 4; c /= 2) {
+    const int c_hi = row_bytes >= 192 * 1024 ? 8 : cl, c_lo = row_bytes >= 192 * 1024 ? 4 : cl;
+    for (int c = c_hi; c >= c_lo; c /= 2) {
       const double n = double((p.vocab / 8 + c - 1) / c) / 128.0;
-      const double singles = (n - 8.0 * double(int64_t(n / 8.0))) / n;
-      if (singles < best - 0.02) {
-        best = singles;
-        cl = c;
+      for (int u = cap ? 8 : 10; u >= 6; u -= 2) {
+        const double singles = (n - double(u) * double(int64_t(n / double(u)))) / n;
+        if (singles < best - 0.02) {
+          best = singles;
+          cl = c;
+          un = u;
+        }
       }
     }
   }
@@ -318,9 +331,12 @@ void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, i
   const char* env_sm = std::getenv("MLLM_GRPO_SMEM");
   if (env_sm) sm = std::atoi(env_sm) != 0 && cl == 1 && aligned16 && ent != 2 && slice_bytes <= 100 * 1024;
   if (sm && !env_th) th = 256;
+  const char* env_un = std::getenv("MLLM_GRPO_L2_UNROLL");
+  if (env_un) un = std::atoi(env_un);
   *cluster = cl;
   *threads = th;
   *smem = sm;
+  *unroll = (un == 6 || un == 10) ? un : 8;
 }
 
 // *taken is false (nothing launched) when logits and dlogits rows do not share their 16-byte phase.
@@ -330,8 +346,10 @@ cudaError_t launch_two_pass(const KernelParams& p, int ent, bool sharded, cudaSt
   if (!*taken) return cudaSuccess;
   int cluster = 1, threads = 256;
   bool smem = false;
-  two_pass_plan(p, ent, sharded, &cluster, &threads, &smem);
-  return sharded ? launch_c<true>(p, ent, cluster, threads, smem, s) : launch_c<false>(p, ent, cluster, threads, smem, s);
+  int unroll = 8;
+  two_pass_plan(p, ent, sharded, &cluster, &threads, &smem, &unroll);
+  return sharded ? launch_c<true>(p, ent, cluster, threads, unroll, smem, s)
+                 : launch_c<false>(p, ent, cluster, threads, unroll, smem, s);
 }
 
 }  // namespace grpo
