@@ -1,18 +1,28 @@
 #!/usr/bin/env python
 """Benchmark of the fused GRPO token loss (fwd+bwd) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1] [--parallelism vocab|token]
+                    [--impl ours|reference]
 
-One step = one forward+backward pass of the loss over one batch of synthetic logits that is
-already resident in HBM.  N=1 runs the Qwen2.5-7B-shaped workload (32768 x 151936 bf16).
-N>1 (launched by torch.distributed.run, one rank per GPU) runs the same global shape
-vocabulary-sharded: V/N columns per rank, one NCCL all-gather of the per-token partials.
-Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of the
-reference's jnp expressions (the reference itself needs JAX, which is not installable here).
+One step = one forward+backward pass of the loss over one batch of synthetic logits that is already
+resident in HBM.  Workloads: cfg0..cfg3 (the benchmark configurations) and cfg4-<tokens> (one point of
+the token-count sweep, e.g. cfg4-65536, cfg4-1048576).  N=1 runs the whole batch on one GPU.  N>1
+(launched by torch.distributed.run, one rank per GPU) runs the same global batch sharded:
+  --parallelism vocab (default): V/N columns per rank, ONE kernel per GPU with the exchange of the
+      per-token partials inside it (peer stores over NVLink); `--vp-mode nccl` selects three kernels
+      with an NCCL all-gather between them instead.
+  --parallelism token: B/N sequences per rank, each through the single-GPU kernel, and one scalar
+      all-reduce of the loss (the reference's dp/fsdp batch sharding).
+Every shard is a slice of the same seeded tensor the 1-GPU run uses.  A batch whose logits exceed
+45 GB per GPU is run as equal row chunks over one buffer (stated in `config`).
+Prints ONE JSON line on rank 0; `extra` holds short runs of the other configurations.
+`--impl reference` times the CPU restatement of the reference's jnp expressions (the reference itself
+needs JAX, which exists neither where this was written nor on the GPU hosts).
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -27,10 +37,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "fused GRPO loss fwd+bwd tokens/s"
-# DRAM bytes per logit element of two_pass_kernel, from one ncu capture of the 2048-row case:
-# (623.2 + 564.8 + 57.5) MB / (2048 * 151936) elements = 4.003 (one bf16 read + one bf16 write).
-NCU_TRAFFIC_PER_ELEMENT = 4.003
 UNIT = "tokens/s"
+# DRAM bytes per logit element the one-kernel step moves (dram__bytes_read + dram__bytes_write of ncu
+# captures on small cases of the same kernels, see profiles/): one bf16 read + one bf16 write.
+NCU_TRAFFIC_PER_ELEMENT = {"two_pass_kernel": 4.003}
+CHUNK_BYTES = 45e9  # largest logits buffer per GPU; bigger batches run as row chunks over one buffer
+DEFAULT_EXTRA = "cfg2,cfg3,cfg4-65536"
 
 
 def parse():
@@ -40,14 +52,22 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="cfg1")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--parallelism", default="vocab", choices=["vocab", "token"],
+                    help="N>1: shard the vocabulary (default) or the sequences")
     ap.add_argument("--cpu-sample-tokens", type=int, default=512)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--extra", default=None,
+                    help="comma-separated workloads measured briefly after the main one and reported under "
+                         f"'extra' (default for the default workload: {DEFAULT_EXTRA}; 'none' to skip)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--vocab", type=int, default=0, help="override the workload's vocabulary size (tuning only)")
     ap.add_argument("--rows", type=int, default=0, help="override the number of sequences (tuning only)")
     ap.add_argument("--vp-mode", default="fused", choices=["fused", "nccl"],
-                    help="N>1: exchange inside the kernel over peer stores, or three kernels + NCCL all-gather")
+                    help="vocab-parallel: exchange inside the kernel over peer stores, or three kernels + NCCL all-gather")
+    ap.add_argument("--fold-lm-head", action="store_true",
+                    help="time the lm_head projection folded into the loss (hidden x weight -> log-probs without "
+                         "logits in HBM) instead of the loss on materialised logits; 1 GPU")
     return ap.parse_args()
 
 
@@ -55,8 +75,8 @@ def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
 class ClockSampler:
@@ -129,7 +149,8 @@ def cpu_baseline(args, w, steps=None, warmup=1):
     from oracle import grpo_oracle as O
 
     nseq = max(1, args.cpu_sample_tokens // 64)
-    sample = synth.scaled(w, n_seqs=nseq, seq_len=64, len_lo=16, len_hi=64, group=min(w.group, nseq))
+    sample = synth.scaled(w, n_seqs=nseq, seq_len=64, len_lo=16, len_hi=64, group=min(w.group, nseq),
+                          half_valid_runs=False)
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     data = synth.make_inputs(sample, seed=1)
@@ -149,62 +170,170 @@ def cpu_baseline(args, w, steps=None, warmup=1):
             "sample": f"{sample.n_tokens} tokens x V={w.vocab} per pass, {reps} passes, torch-CPU restatement + autograd"}
 
 
-def main():
-    args = parse()
-    if args.impl == "reference":
-        return run_reference(args)
+class Job:
+    """Process-wide state of one bench run."""
 
+    def __init__(self, args):
+        self.args = args
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the GRPO loss kernels have no CPU path")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+        self.peaks, self.peak_kind = peaks()
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, x: float) -> float:
+        if self.dist is None:
+            return x
+        t = torch.tensor([x], device=self.dev, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+
+def chunking(w, rows_local_seqs: int, v_local: int):
+    """(sequences per chunk, chunks): the largest divisor of this rank's sequences whose logits fit CHUNK_BYTES."""
+    per_seq = w.seq_len * v_local * 2.0
+    best = 1
+    for c in range(1, rows_local_seqs + 1):
+        if rows_local_seqs % c == 0 and c * per_seq <= CHUNK_BYTES:
+            best = c
+    return best, rows_local_seqs // best
+
+
+def sample_rows(n_rows: int, count: int = 64, seed: int = 7) -> torch.Tensor:
+    gen = torch.Generator().manual_seed(seed)
+    rows = torch.cat([torch.tensor([0, n_rows - 1]), torch.randint(0, n_rows, (max(count - 2, 0),), generator=gen)])
+    return rows.unique()
+
+
+def parity_check(job: Job, w, data, out, mode: str, v_local: int) -> dict:
+    """Sampled rows of the timed buffers against the closed-form CPU oracle: per-token log-prob (abs), entropy
+    (abs) and dlogits (row-relative).  vocab: the rows' column shards are gathered to rank 0, which checks whole
+    rows; token: every rank checks rows of its own and the worst figure is taken."""
+    import numpy as np
+
+    from oracle import grpo_oracle as O
+
+    dist, dev = job.dist, job.dev
+    T = data["token_ids"].shape[1]
+    n_local = data["token_ids"].numel()
+    count = 64 if mode != "token" else max(8, 64 // job.world)
+    rows = sample_rows(n_local, count).to(dev)
+    x = data["logits"].view(n_local, -1)[rows]
+    d = out["dlogits"].view(n_local, -1)[rows]
+    if mode == "vocab":
+        xs = torch.empty(job.world, *x.shape, dtype=x.dtype, device=dev)
+        ds = torch.empty(job.world, *d.shape, dtype=d.dtype, device=dev)
+        dist.all_gather_into_tensor(xs.view(-1), x.contiguous().view(-1))
+        dist.all_gather_into_tensor(ds.view(-1), d.contiguous().view(-1))
+        x = xs.permute(1, 0, 2).reshape(rows.numel(), -1)
+        d = ds.permute(1, 0, 2).reshape(rows.numel(), -1)
+    res = None
+    if mode != "vocab" or job.rank == 0:
+        pick = lambda t: t.reshape(n_local)[rows].double().cpu().numpy()  # noqa: E731
+        advN = data["advantages"][:, None].expand(-1, T).reshape(n_local)
+        an = O.analytic_rows(x.double().cpu().numpy(), data["token_ids"].reshape(n_local)[rows].long().cpu().numpy(),
+                             pick(data["mask"]), pick(advN), pick(data["old_logps"]), pick(data["ref_logps"]),
+                             data["total_valid"], beta=w.beta, epsilon_low=w.epsilon_low,
+                             epsilon_high=w.epsilon_high, softcap=w.softcap)
+        lp_abs = float(np.abs(pick(out["per_token_logps"]) - an["lp"]).max())
+        ent_abs = float(np.abs(pick(out["token_entropy"]) - an["entropy_guard"]).max())
+        dn = d.double().cpu().numpy()
+        rowmax = np.abs(an["dlogits"]).max(axis=1)
+        err = np.abs(dn - an["dlogits"]).max(axis=1)
+        nz = rowmax > 0
+        d_rel = float((err[nz] / rowmax[nz]).max()) if nz.any() else 0.0
+        zero_ok = bool((err[~nz] == 0).all())
+        res = [lp_abs, ent_abs, d_rel, 0.0 if zero_ok else 1.0]
+    if mode == "token" and dist is not None:
+        t = torch.tensor(res, device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res = t.tolist()
+    if res is None:
+        return None
+    total_rows = int(rows.numel()) * (job.world if mode == "token" else 1)
+    return {"rows": total_rows, "lp_abs": res[0], "entropy_abs": res[1], "dlogits_rel": res[2],
+            "zero_rows_exact": res[3] == 0.0, "gates": {"lp_abs": 2e-3, "entropy_abs": 5e-4, "dlogits_rel": 1e-2},
+            "ok": bool(res[0] <= 2e-3 and res[1] <= 5e-4 and res[2] <= 1e-2 and res[3] == 0.0),
+            "against": "closed-form f64 CPU oracle on sampled rows of the timed buffers"}
+
+
+def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> dict:
+    """Measure one workload at this job's GPU count.  main=False: the short form used for `extra`."""
     import mllm_jax_b200 as G
     from mllm_jax_b200 import _lib, synth
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the GRPO loss kernels have no CPU path")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=dev)
-    _lib.load()
-
-    w = synth.CONFIGS[args.workload]
-    if args.vocab:
+    args, world, rank, dev, dist = job.args, job.world, job.rank, job.dev, job.dist
+    w = synth.parse_workload(name)
+    if main and args.vocab:
         w = synth.scaled(w, vocab=args.vocab, name=w.name + f"-V{args.vocab}")
-    if args.rows:
+    if main and args.rows:
         w = synth.scaled(w, n_seqs=args.rows, name=w.name + f"-B{args.rows}")
     cfg = G.LossConfig(epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high, beta=w.beta, softcap=w.softcap)
     N, V = w.n_tokens, w.vocab
+    mode = "single" if world == 1 else args.parallelism
+    if mode == "vocab" and V % world:
+        return {"workload": w.name, "skipped": f"vocabulary {V} does not split over {world} ranks"}
+    if mode == "token" and w.n_seqs % world:
+        return {"workload": w.name, "skipped": f"{w.n_seqs} sequences do not split over {world} ranks"}
+    v_local = V // world if mode == "vocab" else V
+    seqs_local = w.n_seqs // world if mode == "token" else w.n_seqs
+    chunk_seqs, n_chunks = chunking(w, seqs_local, v_local)
+    wc = w
+    if n_chunks > 1:  # the buffer holds one chunk: generate that many sequences only
+        total = chunk_seqs * (world if mode == "token" else 1)
+        wc = synth.scaled(w, n_seqs=total, group=min(w.group, total))
+    rows_chunk = chunk_seqs * w.seq_len  # rows of one launch on this rank
 
-    if world == 1:
-        data = synth.make_inputs(w, seed=args.seed, device=str(dev))
+    exchange = None
+    if mode == "single":
+        data = synth.make_inputs(wc, seed=args.seed, device=str(dev))
         dlogits = torch.empty_like(data["logits"])
-
         first = G.grpo_value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
                                       data["total_valid"], data["old_logps"], data["ref_logps"], cfg=cfg,
                                       dlogits=dlogits)
         plan1 = first["problem"]  # buffers bound once (static shapes); a step relaunches on the same addresses
 
-        def step():
+        def launch():
             plan1.run("mllm_grpo_fwd_bwd", reuse_args=True)
             return first
         parallelism = "single"
+        kernel = "two_pass_kernel (mllm_grpo_fwd_bwd)"
+    elif mode == "token":
+        from mllm_jax_b200.vocab_parallel import TokenParallelLoss
+
+        data = synth.make_inputs(wc, seed=args.seed, device=str(dev), row_shard=(rank, world))
+        dlogits = torch.empty_like(data["logits"])
+        tp = TokenParallelLoss(cfg)
+        first = tp.value_and_grad(data["logits"], data["token_ids"], data["mask"], data["advantages"],
+                                  data["total_valid"], data["old_logps"], data["ref_logps"], dlogits=dlogits)
+        plan1 = first["problem"]
+
+        def launch():
+            plan1.run("mllm_grpo_fwd_bwd", reuse_args=True)
+            first["loss"] = tp.reduce_loss(first["local_loss"])  # the one exchange: a scalar all-reduce
+            return first
+        parallelism = f"token-parallel dp{world}: {seqs_local} sequences per rank, scalar loss all-reduce (NCCL)"
+        kernel = "two_pass_kernel (mllm_grpo_fwd_bwd on this rank's rows)"
     else:
         from mllm_jax_b200.vocab_parallel import VocabParallelLoss
 
-        data = synth.make_inputs(w, seed=args.seed, device=str(dev), vocab_shard=(rank, world))
-        vp = VocabParallelLoss(V, cfg)
-        # exact log-probs of the sharded rows come from one forward of the same exchange
-        p0 = vp.problem(data["logits"], data["token_ids"], data["mask"], data["advantages"], data["total_valid"])
-        vp.forward(p0)
-        lp = p0.per_token_logps.clone()
-        data["old_logps"] = lp + (data["old_logps"] - data["exact_logps"])
-        data["ref_logps"] = lp + (data["ref_logps"] - data["exact_logps"])
+        data = synth.make_inputs(wc, seed=args.seed, device=str(dev), vocab_shard=(rank, world))
         dlogits = torch.empty_like(data["logits"])
-
+        vp = VocabParallelLoss(V, cfg)
         call_args = (data["logits"], data["token_ids"], data["mask"], data["advantages"], data["total_valid"],
                      data["old_logps"], data["ref_logps"])
         vp_mode, vp_note = args.vp_mode, None
@@ -221,144 +350,132 @@ def main():
                 vp_mode = "nccl"
                 vp_note = vp_note or "another rank could not set up the peer exchange buffers"
         if vp_mode == "fused":
-            def step():
+            def launch():
                 return vp.step_fused(plan)
+            kernel = "two_pass_kernel<SHARDED> (mllm_grpo_fwd_bwd_sharded: exchange inside the kernel)"
         else:
-            def step():
+            def launch():
                 return vp.value_and_grad(*call_args, dlogits=dlogits)
+            kernel = "row_stats_kernel + NCCL all-gather + combine_kernel + dlogits_kernel"
         parallelism = f"vocab-parallel tp{world}, exchange: " + (
             "peer stores inside the kernel" if vp_mode == "fused" else "NCCL all-gather between kernels") + (
             f" [{vp_note}]" if vp_note else "")
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    def step():
+        for _ in range(n_chunks):
+            out = launch()
+        return out
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         out = step()
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
+    job.barrier()
+    sampler = ClockSampler(job.local)
+    if rank == 0 and main:
         sampler.start()
         time.sleep(0.15)
     launches0 = _lib.launch_count()
-    barrier()
+    job.barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         out = step()
     ev1.record()
-    barrier()
+    job.barrier()
     launches = _lib.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
-    ms = ev0.elapsed_time(ev1)
-    if dist is not None:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / args.steps
+    clocks = sampler.stop() if rank == 0 and main else None
+    ms_per_step = job.max_over_ranks(ev0.elapsed_time(ev1)) / steps
     value = N / (ms_per_step * 1e-3)
     loss = float(out["loss"].item())
+    status = int(out["problem"].device_status.item())
 
-    # Per-kernel timing of the two streaming passes (same buffers), for the roofline of the dominant one.
-    prob = out["problem"]
-    fwd_entry = "mllm_grpo_fwd" if world == 1 else "mllm_grpo_fwd_partials"
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    t_f, t_b = [], []
-    for i in range(3 + args.steps):
+    # The dominant kernel alone: CUDA events around each launch of the entry point (the kernel plus the
+    # 5 us loss reduction), averaged.
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    t_k = []
+    for i in range(3 + min(steps, 10)):
+        if dist is not None and mode == "vocab":
+            dist.barrier()  # ranks enter the exchanging kernel together, as in the timed loop's steady state
         evs[0].record()
-        prob.run(fwd_entry)
+        launch()
         evs[1].record()
-        prob.run("mllm_grpo_bwd")
-        evs[2].record()
         torch.cuda.synchronize()
         if i >= 3:
-            t_f.append(evs[0].elapsed_time(evs[1]))
-            t_b.append(evs[1].elapsed_time(evs[2]))
-    ms_f, ms_b = sum(t_f) / len(t_f), sum(t_b) / len(t_b)
-    peak, peak_kind = peaks()
-    v_local = V // world
-    bytes_bwd = 4.0 * v_local * N  # read logits + write dlogits, bf16 (zero rows counted in full)
-    bytes_fwd = 2.0 * v_local * N
-    ach_b = bytes_bwd / (ms_b * 1e-3) / 1e9
-    sweeps = {"fwd_kernel": {"name": "row_stats_kernel", "ms_per_launch": ms_f,
-                             "achieved": bytes_fwd / (ms_f * 1e-3) / 1e9,
-                             "frac": bytes_fwd / (ms_f * 1e-3) / 1e9 / peak},
-              "bwd_kernel": {"name": "dlogits_kernel", "ms_per_launch": ms_b, "achieved": ach_b,
-                             "frac": ach_b / peak}}
-    bytes_step = 6.0 * v_local * N
-    if world == 1:
-        # One kernel does the whole step (loss_reduce_kernel adds ~5 us): time the entry point itself.
+            t_k.append(evs[0].elapsed_time(evs[1]))
+    ms_launch = job.max_over_ranks(sum(t_k) / len(t_k))
+    peak = float(job.peaks["hbm_gbs"])
+    bytes_launch = 6.0 * v_local * rows_chunk   # algorithmic: logits read twice + dlogits written once
+    bytes_min = 4.0 * v_local * rows_chunk      # what has to cross HBM when the second read is served on chip
+    ach = bytes_launch / (ms_launch * 1e-3) / 1e9
+    one_kernel = "two_pass_kernel" in kernel
+    roofline = {
+        "bound": "hbm", "kernel": kernel, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+        "peak_kind": job.peak_kind, "ms_per_launch": ms_launch, "algorithmic_bytes_per_launch": bytes_launch,
+        "traffic": NCU_TRAFFIC_PER_ELEMENT["two_pass_kernel"] * v_local * rows_chunk if one_kernel else None,
+        "traffic_note": "dram__bytes_read + dram__bytes_write per logit element from ncu captures of small cases of "
+                        "the same kernel (profiles/), scaled by the elements of one launch: traffic grows in proportion",
+        "note": "algorithmic = logits read twice + dlogits written once (6*V*N per GPU); the kernel's second read is "
+                "served on chip and zero-gradient rows are not re-read, so its minimum DRAM traffic is 4*V*N and "
+                "frac can exceed 1; frac_min_dram is the physical view",
+        "min_dram_bytes_per_launch": bytes_min,
+        "achieved_min_dram": bytes_min / (ms_launch * 1e-3) / 1e9,
+        "frac_min_dram": bytes_min / (ms_launch * 1e-3) / 1e9 / peak,
+        "frac_of_8TBs": ach / 8000.0,
+        "step": {"ms_per_step": ms_per_step, "launches_per_step": n_chunks,
+                 "frac": 6.0 * v_local * rows_chunk * n_chunks / (ms_per_step * 1e-3) / 1e9 / peak,
+                 "frac_min_dram": 4.0 * v_local * rows_chunk * n_chunks / (ms_per_step * 1e-3) / 1e9 / peak},
+    }
+
+    if mode == "vocab" and one_kernel:
+        # Exchange overhead: the same shard, taken as a vocabulary of its own, through the exchange-free entry point.
+        local_ids = data["token_ids"] % v_local
+        solo = G.grpo_value_and_grad(data["logits"], local_ids, data["mask"], data["advantages"],
+                                     data["total_valid"], data["old_logps"], data["ref_logps"], cfg=cfg,
+                                     dlogits=dlogits)["problem"]
         t_s = []
-        for i in range(3 + args.steps):
+        for i in range(3 + min(steps, 10)):
             evs[0].record()
-            prob.run("mllm_grpo_fwd_bwd")
+            solo.run("mllm_grpo_fwd_bwd", reuse_args=True)
             evs[1].record()
             torch.cuda.synchronize()
             if i >= 3:
                 t_s.append(evs[0].elapsed_time(evs[1]))
-        ms_k = sum(t_s) / len(t_s)
-        mode = os.environ.get("MLLM_GRPO_FWD_BWD_MODE", "auto")
-        ach = bytes_step / (ms_k * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": f"single-kernel fwd+bwd (mode {mode}: two_pass_kernel)",
-                    "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": peak_kind,
-                    "traffic": (NCU_TRAFFIC_PER_ELEMENT * v_local * N if (V == 151936 and mode == "auto") else None),
-                    "traffic_note": "dram__bytes_read+write of one ncu capture on cfg0 (2048 rows, same V): 623.2 MB "
-                                    "read + 564.8 MB written + 57.5 MB of gradient still dirty in L2, scaled by "
-                                    "rows (traffic grows in proportion)",
-                    "ms_per_launch": ms_k, "algorithmic_bytes_per_launch": bytes_step,
-                    "note": "algorithmic = logits read twice + dlogits written once (6*V*N); the kernel's second "
-                            "read is served by L2 and zero-gradient rows are not re-read, so its minimum DRAM "
-                            "traffic is 4*V*N and frac can exceed 1",
-                    "min_dram_bytes_per_launch": 4.0 * v_local * N,
-                    "achieved_min_dram": 4.0 * v_local * N / (ms_k * 1e-3) / 1e9,
-                    "frac_min_dram": 4.0 * v_local * N / (ms_k * 1e-3) / 1e9 / peak,
-                    "frac_of_8TBs": ach / 8000.0, "separate_sweeps": sweeps}
-    else:
-        roofline = {"bound": "hbm", "kernel": "dlogits_kernel (backward sweep of this rank's shard)",
-                    "achieved": ach_b, "peak": peak, "unit": "GB/s", "frac": ach_b / peak, "peak_kind": peak_kind,
-                    "traffic": None, "ms_per_launch": ms_b, "algorithmic_bytes_per_launch": bytes_bwd,
-                    "separate_sweeps": sweeps,
-                    "step": {"algorithmic_bytes_per_gpu": bytes_step,
-                             "achieved_per_gpu": bytes_step / (ms_per_step * 1e-3) / 1e9,
-                             "frac": bytes_step / (ms_per_step * 1e-3) / 1e9 / peak}}
+        ms_solo = job.max_over_ranks(sum(t_s) / len(t_s))
+        exchange = {"ms_sharded_launch": ms_launch, "ms_same_shard_without_exchange": ms_solo,
+                    "overhead_ms": ms_launch - ms_solo, "overhead_frac": (ms_launch - ms_solo) / ms_launch,
+                    "payload_bytes_per_token_per_rank": 32 * world,
+                    "note": "same rows and columns through mllm_grpo_fwd_bwd (plan of an unsharded row of that "
+                            "length) against mllm_grpo_fwd_bwd_sharded; each rank stores 4 (float, epoch) words "
+                            "of 8 bytes per token into every rank's buffer"}
+        out = launch()  # the timed path's outputs again (the solo run overwrote dlogits)
+        torch.cuda.synchronize()
+
+    parity = parity_check(job, w, data, out, mode, v_local)
 
     e2e = None
-    if not args.no_e2e:
-        if world == 1:
-            e2e = measure_e2e(data, lambda: G.grpo_value_and_grad(
-                data["logits"], data["token_ids"], data["mask"], data["advantages"], data["total_valid"],
-                data["old_logps"], data["ref_logps"], cfg=cfg, dlogits=dlogits), args)
-        else:
-            e2e = measure_e2e(data, step, args, dist, dev)
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        del data, dlogits
-        torch.cuda.empty_cache()
-        cpu = cpu_baseline(args, w)
-
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 in / f32 accumulate", "data": "synthetic",
-            "config": {"workload": w.name, "rows": N, "vocab": V, "global_batch": w.n_seqs, "seq_len": w.seq_len,
-                       "parallelism": parallelism, "l2": "inputs (%.1f GB per GPU) exceed the 126 MB L2" %
-                       (2.0 * v_local * N / 1e9), "mask_valid_fraction": prob.mask.mean().item(),
-                       "epsilon": [w.epsilon_low, w.epsilon_high], "beta": w.beta, "softcap": w.softcap},
-            "loss": loss, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
-            "clocks": clocks,
-        }))
+    if main and not args.no_e2e and n_chunks == 1:
+        e2e = measure_e2e(data, launch, args, job)
+    result = {
+        "workload": w.name, "rows": N, "vocab": V, "ms_per_step": ms_per_step, "value": value,
+        "valid_tokens_per_s": value * float(data["mask"].mean().item()), "loss": loss, "device_status": status,
+        "parallelism": parallelism, "roofline": roofline, "exchange": exchange, "parity": parity, "e2e": e2e,
+        "gpu_launches": launches, "clocks": clocks, "steps": steps,
+        "config": {"workload": w.name, "rows": N, "vocab": V, "global_batch": w.n_seqs, "seq_len": w.seq_len,
+                   "parallelism": parallelism,
+                   "l2": "inputs (%.1f GB per GPU per launch) exceed the 126 MB L2" % (2.0 * v_local * rows_chunk / 1e9),
+                   "chunks": None if n_chunks == 1 else
+                   f"{n_chunks} launches per step over ONE buffer of {rows_chunk} rows ({2.0 * v_local * rows_chunk / 1e9:.1f} GB "
+                   f"of logits per GPU): the full batch does not fit beside its gradient",
+                   "mask_valid_fraction": float(data["mask"].mean().item()),
+                   "epsilon": [w.epsilon_low, w.epsilon_high], "beta": w.beta, "softcap": w.softcap},
+    }
+    return result
 
 
-def measure_e2e(data, step_fn, args, dist=None, dev=None):
+def measure_e2e(data, step_fn, args, job: Job):
     """Same metric through the public API with HOST buffers: per step, copy the step's inputs (this
     rank's shard when N > 1) from pinned host memory, run fwd+bwd through `step_fn`, read the loss and
     the per-token log-probs back.  Time = max over ranks."""
+    dist, dev = job.dist, job.dev
     names = ("logits", "token_ids", "mask", "advantages", "old_logps", "ref_logps")
     host = {}
     try:
@@ -368,7 +485,7 @@ def measure_e2e(data, step_fn, args, dist=None, dev=None):
     except RuntimeError as e:  # not enough pinnable host memory
         return {"value": None, "unit": UNIT, "error": str(e)[:120]}
     torch.cuda.synchronize()
-    N = data["token_ids"].numel()
+    n_local = data["token_ids"].numel()
     lp_host = torch.empty(data["token_ids"].shape, dtype=torch.float32, pin_memory=True)
     loss_host = torch.empty((), dtype=torch.float32, pin_memory=True)
     steps = max(2, min(args.steps, 5))
@@ -377,9 +494,7 @@ def measure_e2e(data, step_fn, args, dist=None, dev=None):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for i in range(1 + steps):
         if i == 1:
-            if dist is not None:
-                dist.barrier()
-            torch.cuda.synchronize()
+            job.barrier()
             ev0.record()
         for k in names:
             data[k].copy_(host[k], non_blocking=True)
@@ -388,21 +503,68 @@ def measure_e2e(data, step_fn, args, dist=None, dev=None):
         loss_host.copy_(out["loss"], non_blocking=True)
         torch.cuda.synchronize()
     ev1.record()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ms = ev0.elapsed_time(ev1)
-    world = 1
-    if dist is not None:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        world = dist.get_world_size()
+    job.barrier()
+    ms = job.max_over_ranks(ev0.elapsed_time(ev1))
+    world = job.world
+    token_mode = world > 1 and args.parallelism == "token"
     sec = ms * 1e-3 / steps
-    return {"value": N / sec, "unit": UNIT, "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
-            "ms_per_step": sec * 1e3, "steps": steps,
+    return {"value": n_local * (world if token_mode else 1) / sec, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
+            "d2h_bytes_per_step": d2h * world, "ms_per_step": sec * 1e3, "steps": steps,
             "note": "every rank copies its logits shard over its own PCIe link each step; dlogits stay on the "
                     "device for the lm_head backward"}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.fold_lm_head:
+        from mllm_jax_b200 import lm_head_bench
+
+        return lm_head_bench.main(args)
+
+    from mllm_jax_b200 import _lib, synth
+
+    job = Job(args)
+    _lib.load()
+    res = run_workload(job, args.workload, args.steps, args.warmup, main=True)
+    if "skipped" in res:
+        raise SystemExit(res["skipped"])
+    extra_names = args.extra if args.extra is not None else (DEFAULT_EXTRA if args.workload == "cfg1" else "none")
+    extra = []
+    for name in [n for n in extra_names.split(",") if n and n != "none" and n != args.workload]:
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            r = run_workload(job, name, steps=5, warmup=3, main=False)
+        except torch.OutOfMemoryError as exc:
+            r = {"workload": name, "skipped": f"out of device memory ({str(exc)[:60]})"}
+            torch.cuda.empty_cache()
+        keep = ("workload", "rows", "vocab", "ms_per_step", "value", "valid_tokens_per_s", "loss", "parallelism",
+                "parity", "exchange", "skipped", "device_status")
+        e = {k: r[k] for k in keep if k in r}
+        if "roofline" in r:
+            rf = r["roofline"]
+            e.update(frac=rf["step"]["frac"], frac_min_dram=rf["step"]["frac_min_dram"], ms_per_launch=rf["ms_per_launch"],
+                     launches_per_step=rf["step"]["launches_per_step"], chunks=r["config"]["chunks"])
+        extra.append(e)
+
+    cpu = None
+    if job.rank == 0 and job.world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(args, synth.parse_workload(args.workload))
+    if job.dist is not None:
+        job.dist.barrier()
+        job.dist.destroy_process_group()
+    if job.rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": job.world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 in / f32 accumulate", "data": "synthetic",
+            "config": res["config"], "loss": res["loss"], "device_status": res["device_status"],
+            "valid_tokens_per_s": res["valid_tokens_per_s"], "roofline": res["roofline"], "exchange": res["exchange"],
+            "parity": res["parity"], "cpu_baseline": cpu, "e2e": res["e2e"], "gpu_launches": res["gpu_launches"],
+            "clocks": res["clocks"], "extra": extra,
+        }))
 
 
 def run_reference(args):
@@ -411,7 +573,7 @@ def run_reference(args):
         return
     from mllm_jax_b200 import synth
 
-    w = synth.CONFIGS[args.workload]
+    w = synth.parse_workload(args.workload)
     t_all = time.perf_counter()
     cb = cpu_baseline(args, w, steps=args.steps, warmup=min(args.warmup, 2))
     value = cb["value"]
@@ -419,7 +581,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_pass"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "sample": cb["sample"]},
+        "config": {"workload": w.name, "sample": cb["sample"],
+                   "note": "the reference's jnp path needs JAX, which is installed neither on the build host nor on "
+                           "the GPU hosts (probed); this arm times the line-for-line torch-CPU restatement"},
         "cpu_baseline": cb,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t_all,

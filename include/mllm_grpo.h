@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define MLLM_GRPO_ABI_VERSION 2
+#define MLLM_GRPO_ABI_VERSION 3
 #define MLLM_GRPO_MAX_SHARDS 8
 
 typedef enum mllm_grpo_status {
@@ -56,7 +56,8 @@ typedef enum mllm_grpo_status {
 /* Bits the kernels may OR into *args->device_status (an int32 in device memory,
  * read by the host after it has synchronised the stream itself). */
 #define MLLM_GRPO_DEV_ID_CLAMPED 1   /* a chosen id fell outside [0, vocab_total) and was clamped */
-#define MLLM_GRPO_DEV_WAIT_TIMEOUT 2 /* a bounded wait on a peer flag ran out */
+#define MLLM_GRPO_DEV_WAIT_TIMEOUT 2 /* a bounded wait on a peer ran out: the call's loss is NaN, its dlogits of
+                                        the affected rows are zero, and the bit stays set until the caller clears it */
 
 /* One struct serves every entry point; each entry point documents the fields
  * it reads.  Zero-initialise it, set struct_size = sizeof(mllm_grpo_args). */
@@ -120,11 +121,22 @@ typedef struct mllm_grpo_args {
                                                 exchange buffer (mllm_grpo_exchange_bytes each, zeroed once);
                                                 entry shard_rank is this rank's own buffer */
   int32_t exchange_epoch; /* > 0, the same on every rank, +1 on every call that uses the buffers */
-  int32_t reserved1;
+  int32_t peer_wait_ms;   /* how long a row may wait for the other ranks' partials; 0 = 2000 ms.  This is the
+                             skew between ranks the call tolerates (a rank held up by a checkpoint, a data
+                             loader or a collector for longer than this poisons the step, see below) */
 
   /* ---- per-sample monitors of mllm_grpo_entropy_stats ---- */
   float* sample_entropy;        /* [B] sum_t H_t m_t / sum_t m_t                      (train_modules :141-143) */
   float* sample_entropy_window; /* [B] the same over valid tokens number 4..100 of a sample (:148-157) */
+
+  /* ---- gradient of the entropy (mllm_grpo_bwd only) ---- */
+  const float* entropy_cotangent; /* [B*T] or NULL: cotangent of token_entropy.  When given, mllm_grpo_bwd adds
+                                     cot_t * dH_t/dlogits to dlogits (the -entropy_coef * entropy term of
+                                     plugins/training/ppo/module.py:140 reaches the logits this way); it is
+                                     not multiplied by grad_scale, which belongs to the loss */
+  float* lse_scaled;              /* [B*T] or NULL: log-sum-exp of the row divided by the temperature, written
+                                     by the forward when non-NULL; the entropy gradient reads it when
+                                     temperature != 1 (at temperature 1 it equals lse and may stay NULL) */
 } mllm_grpo_args;
 
 #define MLLM_GRPO_FLAG_SKIP_ENTROPY 1 /* do not compute token_entropy (saves one FMA per element) */
@@ -173,25 +185,26 @@ int mllm_grpo_combine(const mllm_grpo_args* args, void* stream);
 
 /* Vocabulary-sharded forward AND backward in one kernel per GPU, with the exchange inside it.
  * Each rank (one process per GPU) calls it on its own column shard at the same time.  A CTA
- * streams its row shard once, pushes (max, sumexp, sum e*y, chosen-or-0) with plain peer stores
- * over NVLink into every rank's exchange buffer followed by a release flag, waits (bounded) for
- * the other ranks' flags in its OWN buffer, merges, runs the per-token epilogue and streams the
- * row shard a second time (an L2 hit) to write its dlogits columns.  This is the fused form of
- * mllm_grpo_fwd_partials -> all-gather -> mllm_grpo_combine -> mllm_grpo_bwd, i.e. of the
- * all-reduce(max)/all-reduce(sum) XLA inserts for tp-sharded logits (MLLM_JAX/utils.py:245).
- * Every output of mllm_grpo_fwd is replicated on every rank.  Needs temperature == 1 when the
- * entropy is requested, n_shards <= MLLM_GRPO_MAX_SHARDS, peer access enabled between the
- * devices, and the same exchange_epoch on all ranks (buffers are double-buffered by its parity,
- * so consecutive calls need no barrier between them).  A rank whose peers never arrive gives up
- * after a bounded wait and sets MLLM_GRPO_DEV_WAIT_TIMEOUT in *device_status. */
+ * streams its row shard once and pushes (max, sumexp, sum e*y, chosen-or-0) into every rank's
+ * exchange buffer with plain 8-byte peer stores over NVLink; every word carries one float and the
+ * call's epoch, so a word that shows the epoch is complete by itself (no separate flag, no fence).
+ * The CTA then polls its OWN buffer (bounded) until all ranks' words show the epoch, merges, runs
+ * the per-token epilogue and streams the row shard a second time (served on chip) to write its
+ * dlogits columns.  This is the fused form of mllm_grpo_fwd_partials -> all-gather ->
+ * mllm_grpo_combine -> mllm_grpo_bwd, i.e. of the all-reduce(max)/all-reduce(sum) XLA inserts for
+ * tp-sharded logits (MLLM_JAX/utils.py:245).  Every output of mllm_grpo_fwd is replicated on every
+ * rank.  Needs temperature == 1 when the entropy is requested, n_shards <= MLLM_GRPO_MAX_SHARDS,
+ * every rank's exchange buffer mapped on this device with store access (cuMem / symmetric-memory
+ * mappings; NVLink multicast is not used), the same exchange_epoch on all ranks (buffers are
+ * double-buffered by its parity, so consecutive calls need no barrier between them) and a
+ * non-NULL device_status.
+ * Failure behaviour: a row whose peers' words do not arrive within peer_wait_ms raises
+ * MLLM_GRPO_DEV_WAIT_TIMEOUT in *device_status; from then on no CTA of this call (or of a later
+ * call that starts with the bit still set) waits any more, so a dead peer costs about one wait
+ * limit per call, not one per row.  Every row that gave up gets per_token_logps = NaN and a zero
+ * dlogits row, and the call's loss is NaN, so a poisoned step cannot be consumed unnoticed.  The
+ * caller clears the bit before the next healthy call. */
 int mllm_grpo_fwd_bwd_sharded(const mllm_grpo_args* args, void* stream);
-
-/* Lets kernels on the CURRENT device store into memory of peer_device (cudaDeviceEnablePeerAccess;
- * "already enabled" counts as success).  Call once per peer before mllm_grpo_fwd_bwd_sharded when
- * the exchange buffers were mapped by a route that does not enable it for the current device
- * (CUDA IPC handles opened under the owner's device do not).  MLLM_GRPO_ERR_UNSUPPORTED if the
- * two devices cannot reach each other. */
-int mllm_grpo_enable_peer_access(int peer_device);
 
 /* Bytes of one rank's exchange buffer for n_tokens = B*T and n_shards ranks. */
 int64_t mllm_grpo_exchange_bytes(int64_t n_tokens, int32_t n_shards);
@@ -262,6 +275,14 @@ int64_t mllm_ppo_value_workspace_bytes(int64_t n_seqs, int64_t seq_rows);
 
 /* Bytes of loss_terms scratch a problem of n_tokens = B*T needs. */
 int64_t mllm_grpo_workspace_bytes(int64_t n_tokens);
+
+/* Tuning / test hook: forces how mllm_grpo_fwd_bwd and mllm_grpo_fwd_bwd_sharded run in this process, until
+ * called again.  sweeps != 0: mllm_grpo_fwd_bwd takes the separate forward and backward kernels.  cluster
+ * (1/2/4/8 CTAs per row), threads (64/128/256/512 per CTA), load_batch (6/8/10 vectors per thread) and staged
+ * (0/1: row shard held in shared memory) override the plan the library derives from the row length; 0 (-1 for
+ * staged) leaves a field automatic.  Combinations a kernel cannot run fall back to the nearest one that it can.
+ * Production code never needs this: the automatic plan is the measured one. */
+int mllm_grpo_set_plan_override(int sweeps, int cluster, int threads, int load_batch, int staged);
 
 int mllm_grpo_abi_version(void);
 const char* mllm_grpo_status_string(int status);

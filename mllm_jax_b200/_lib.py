@@ -19,7 +19,7 @@ EXPORTS = (
     "mllm_grpo_fwd", "mllm_grpo_bwd", "mllm_grpo_fwd_bwd", "mllm_grpo_fwd_partials", "mllm_grpo_combine",
     "mllm_grpo_logprobs", "mllm_grpo_workspace_bytes", "mllm_grpo_abi_version", "mllm_grpo_status_string",
     "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count", "mllm_grpo_fwd_static_scratch",
-    "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_exchange_bytes", "mllm_grpo_enable_peer_access",
+    "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_exchange_bytes", "mllm_grpo_set_plan_override",
     "mllm_grpo_entropy_stats", "mllm_grpo_scale_grad", "mllm_ppo_value_loss", "mllm_ppo_value_workspace_bytes",
 )
 
@@ -43,8 +43,9 @@ class GrpoArgs(C.Structure):
         ("partials", C.c_void_p), ("gathered_partials", C.c_void_p), ("n_shards", C.c_int32),
         ("shard_rank", C.c_int32),
         ("device_status", C.c_void_p),
-        ("peer_exchange", C.c_void_p * 8), ("exchange_epoch", C.c_int32), ("reserved1", C.c_int32),
+        ("peer_exchange", C.c_void_p * 8), ("exchange_epoch", C.c_int32), ("peer_wait_ms", C.c_int32),
         ("sample_entropy", C.c_void_p), ("sample_entropy_window", C.c_void_p),
+        ("entropy_cotangent", C.c_void_p), ("lse_scaled", C.c_void_p),
     ]
 
 
@@ -94,8 +95,8 @@ def load():
     lib.mllm_ppo_value_workspace_bytes.restype = C.c_int64
     lib.mllm_grpo_workspace_bytes.argtypes = [C.c_int64]
     lib.mllm_grpo_workspace_bytes.restype = C.c_int64
-    lib.mllm_grpo_enable_peer_access.argtypes = [C.c_int]
-    lib.mllm_grpo_enable_peer_access.restype = C.c_int
+    lib.mllm_grpo_set_plan_override.argtypes = [C.c_int] * 5
+    lib.mllm_grpo_set_plan_override.restype = C.c_int
     lib.mllm_grpo_exchange_bytes.argtypes = [C.c_int64, C.c_int32]
     lib.mllm_grpo_exchange_bytes.restype = C.c_int64
     lib.mllm_grpo_abi_version.restype = C.c_int
@@ -119,3 +120,21 @@ def call(name: str, args, stream: int) -> None:
 
 def launch_count() -> int:
     return int(load().mllm_grpo_launch_count())
+
+
+class plan_override:
+    """Context manager over mllm_grpo_set_plan_override (tuning and tests): forces the separate sweeps,
+    or the cluster size / thread count / load batch / shared-memory staging of the one-kernel path, for the
+    calls made inside the block; the automatic plan is restored on exit."""
+
+    def __init__(self, sweeps: bool = False, cluster: int = 0, threads: int = 0, load_batch: int = 0,
+                 staged: int = -1):
+        self.values = (int(bool(sweeps)), int(cluster), int(threads), int(load_batch), int(staged))
+
+    def __enter__(self):
+        load().mllm_grpo_set_plan_override(*self.values)
+        return self
+
+    def __exit__(self, *exc):
+        load().mllm_grpo_set_plan_override(0, 0, 0, 0, -1)
+        return False

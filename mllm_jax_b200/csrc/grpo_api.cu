@@ -1,15 +1,14 @@
 // C-ABI layer: argument validation, mllm_grpo_args -> KernelParams, kernel selection.
 // Every entry point is asynchronous on the caller's stream and allocates nothing.
 #include <atomic>
-#include <cstdlib>
 #include <cstring>
-#include <string>
 
 #include "grpo_launch.h"
 
 namespace grpo {
 
 static std::atomic<int64_t> g_launches{0};
+static std::atomic<int> g_force_sweeps{0};  // tuning / test hook: mllm_grpo_fwd_bwd as two separate sweeps
 static thread_local char g_last_error[256] = {0};
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
@@ -65,7 +64,7 @@ static int validate(const mllm_grpo_args* a, unsigned need, KernelParams* k) {
   if (!aligned(a->logits, 2) || !aligned(a->dlogits, 2)) return MLLM_GRPO_ERR_ALIGNMENT;
   const void* f32s[] = {a->chosen_ids, a->mask, a->advantages, a->old_logps, a->ref_logps, a->total_valid_dev,
                         a->grad_scale_dev, a->per_token_logps, a->token_entropy, a->lse, a->grad_coef, a->loss,
-                        a->loss_terms, a->device_status};
+                        a->loss_terms, a->device_status, a->entropy_cotangent, a->lse_scaled};
   for (const void* q : f32s)
     if (!aligned(q, 4)) return MLLM_GRPO_ERR_ALIGNMENT;
   if (!aligned(a->partials, 16) || !aligned(a->gathered_partials, 16)) return MLLM_GRPO_ERR_ALIGNMENT;
@@ -97,6 +96,8 @@ static int validate(const mllm_grpo_args* a, unsigned need, KernelParams* k) {
   k->per_token_logps = a->per_token_logps;
   k->token_entropy = a->token_entropy;
   k->lse = a->lse;
+  k->lse_scaled = a->lse_scaled;
+  k->entropy_cotangent = nullptr;  // only mllm_grpo_bwd honours it
   k->grad_coef = a->grad_coef;
   k->loss = a->loss;
   k->loss_terms = a->loss_terms;
@@ -107,6 +108,7 @@ static int validate(const mllm_grpo_args* a, unsigned need, KernelParams* k) {
   k->device_status = a->device_status;
   k->shard_rank = a->shard_rank;
   k->exchange_epoch = a->exchange_epoch;
+  k->peer_wait_ns = (a->peer_wait_ms > 0 ? static_cast<unsigned long long>(a->peer_wait_ms) : 2000ull) * 1000000ull;
   for (int q = 0; q < MLLM_GRPO_MAX_SHARDS; ++q) k->peer_words[q] = nullptr;
   return MLLM_GRPO_OK;
 }
@@ -140,6 +142,13 @@ int mllm_grpo_bwd(const mllm_grpo_args* args, void* stream) {
   KernelParams k;
   int st = validate(args, kLogits | kIds | kResiduals | kDlogits, &k);
   if (st) return st;
+  if (args->entropy_cotangent) {
+    // needs the forward's token_entropy, its lse_scaled when temperature != 1, and vector-aligned rows
+    if (!args->token_entropy || (args->temperature != 1.0f && !args->lse_scaled)) return MLLM_GRPO_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(args->logits) ^ reinterpret_cast<uintptr_t>(args->dlogits)) & 15)
+      return MLLM_GRPO_ERR_UNSUPPORTED;
+    k.entropy_cotangent = args->entropy_cotangent;
+  }
   cudaError_t e = launch_dlogits(k, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail_cuda(e);
   return MLLM_GRPO_OK;
@@ -153,18 +162,10 @@ int mllm_grpo_fwd_bwd(const mllm_grpo_args* args, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   bool taken = false;
   cudaError_t e = cudaSuccess;
-  // Implementation choice.  Default ("auto"): both passes in one kernel with the second read served
-  // by L2, long rows split over a cluster (MLLM_GRPO_L2_CLUSTER / MLLM_GRPO_L2_THREADS override the
-  // plan).  MLLM_GRPO_FWD_BWD_MODE = "cluster" selects the row-resident kernel (row held in
-  // distributed shared memory, TMA in and out), "sweeps" the separate forward and backward kernels.
-  const char* mode = std::getenv("MLLM_GRPO_FWD_BWD_MODE");
-  const std::string m = mode ? mode : "auto";
+  // Both passes in one kernel, the second read served on chip (grpo_twopass.cu); the separate sweeps
+  // serve row pairs whose logits and dlogits do not share their 16-byte phase.
   const int ent = entropy_mode(args);
-  if (m == "cluster") {
-    e = launch_fused(k, ent, s, &taken);
-  } else if (m != "sweeps") {
-    e = launch_two_pass(k, ent, false, s, &taken);
-  }
+  if (!g_force_sweeps.load(std::memory_order_relaxed)) e = launch_two_pass(k, ent, false, s, &taken);
   if (e != cudaSuccess) return fail_cuda(e);
   if (taken) {
     e = launch_loss_reduce(k, s);
@@ -226,20 +227,10 @@ int mllm_grpo_entropy_stats(const mllm_grpo_args* args, void* stream) {
   return e == cudaSuccess ? MLLM_GRPO_OK : fail_cuda(e);
 }
 
-int mllm_grpo_enable_peer_access(int peer_device) {
-  int dev = -1, can = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return MLLM_GRPO_ERR_NO_DEVICE;
-  if (peer_device == dev) return MLLM_GRPO_OK;
-  if (cudaDeviceCanAccessPeer(&can, dev, peer_device) != cudaSuccess || !can) {
-    (void)cudaGetLastError();
-    return MLLM_GRPO_ERR_UNSUPPORTED;
-  }
-  const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
-  if (e == cudaErrorPeerAccessAlreadyEnabled) {
-    (void)cudaGetLastError();
-    return MLLM_GRPO_OK;
-  }
-  return e == cudaSuccess ? MLLM_GRPO_OK : fail_cuda(e);
+int mllm_grpo_set_plan_override(int sweeps, int cluster, int threads, int load_batch, int staged) {
+  g_force_sweeps = sweeps != 0;
+  set_two_pass_override(cluster, threads, load_batch, staged);
+  return MLLM_GRPO_OK;
 }
 
 int64_t mllm_grpo_exchange_bytes(int64_t n_tokens, int32_t n_shards) {
@@ -257,6 +248,7 @@ int mllm_grpo_fwd_bwd_sharded(const mllm_grpo_args* args, void* stream) {
     return MLLM_GRPO_ERR_BAD_ATTRIBUTE;
   const int ent = entropy_mode(args);
   if (ent == 2) return MLLM_GRPO_ERR_UNSUPPORTED;  // sharded entropy needs temperature 1
+  if (args->device_status == nullptr) return MLLM_GRPO_ERR_NULL_POINTER;  // the waits report through it
   for (int q = 0; q < args->n_shards; ++q) {
     if (args->peer_exchange[q] == nullptr) return MLLM_GRPO_ERR_NULL_POINTER;
     if (!aligned(args->peer_exchange[q], 16)) return MLLM_GRPO_ERR_ALIGNMENT;

@@ -39,6 +39,8 @@ struct KernelParams {
   float* per_token_logps;
   float* token_entropy;
   float* lse;
+  float* lse_scaled;  // optional: log-sum-exp of y/temperature (residual of the entropy gradient)
+  const float* entropy_cotangent;  // optional, backward sweep only
   float* grad_coef;
   float* loss;
   float* loss_terms;
@@ -51,6 +53,7 @@ struct KernelParams {
   unsigned long long* peer_words[8];  // [2 parities][n_shards senders][N tokens][4] (float, epoch) words
   int shard_rank;
   int exchange_epoch;
+  unsigned long long peer_wait_ns;  // limit of one wait for the other ranks' partials
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -282,6 +285,14 @@ __device__ __forceinline__ TokenOut token_epilogue_core(const KernelParams& p, c
   o.loss_term = m * term;
   o.grad_coef = m * w * p.inv_temperature;
   return o;
+}
+
+// Log-sum-exp of y/temperature (residual of the entropy gradient): the row's lse at temperature 1, from the
+// second pair of sums otherwise; NaN when those were not accumulated (temperature != 1 without the entropy).
+template <int ENT>
+__device__ __forceinline__ float scaled_lse(const KernelParams& p, const RowStats& st, float lse) {
+  if (ENT == 2) return st.M * p.inv_temperature + logf(st.S2);
+  return p.inv_temperature == 1.0f ? lse : __int_as_float(0x7fc00000);
 }
 
 __device__ __forceinline__ TokenSide load_token_side(const KernelParams& p, int64_t n, int64_t b) {

@@ -27,8 +27,7 @@ cudaError_t launch_two_pass(const KernelParams& p, int ent, bool sharded, cudaSt
 // Per-sample entropy monitors (grpo_monitors.cu).
 cudaError_t launch_entropy_stats(const float* H, const float* mask, int64_t B, int64_t T, float* ent, float* ent_win,
                                  cudaStream_t s);
-// Row-resident fused forward+backward (grpo_fused.cu).  *taken is false when the problem does not
-// meet its alignment / size conditions; nothing is launched then and the caller uses the two sweeps.
-cudaError_t launch_fused(const KernelParams& p, int ent, cudaStream_t s, bool* taken);
+// Forced plan of launch_two_pass (tuning / test hook); 0 (-1 for staged) = automatic.
+void set_two_pass_override(int cluster, int threads, int load_batch, int staged);
 
 }  // namespace grpo

@@ -246,6 +246,33 @@ __device__ __forceinline__ RowStats row_pass1(const uint16_t* row16, int64_t V, 
     st.S2 = warp_sum(lane < NW ? red[96 + lane] * sb2 : 0.f);
     st.U2 = warp_sum(lane < NW ? red[128 + lane] * sb2 : 0.f);
   }
+  // A logit of -inf has probability 0 but poisons the entropy sums with 0 * -inf.  The reference's
+  // p*log(p + 1e-9) is 0 there (MLLM_JAX/train_modules/__init__.py:138), so such a row (rare: every
+  // thread sees the same NaN and takes the branch together) sums e*y once more with p == 0 skipped.
+  if ((ENT == 1 && st.U != st.U) || (ENT == 2 && st.U2 != st.U2)) {
+    const float scale = ENT == 2 ? k2 : kLog2e;
+    const float mk = st.M * scale;
+    float u = 0.f;
+    for (int64_t j = tid; j < V; j += THREADS) {
+      uint16_t raw;
+      if (LD == 3) {
+        raw = row16[j];
+      } else {
+        asm volatile("ld.global.u16 %0, [%1];" : "=h"(raw) : "l"(row16 + j));
+      }
+      const float x = __uint_as_float(uint32_t(raw) << 16);
+      const float y = CAP ? sc.y(x) : x;
+      const float e = ex2f(fmaf(y, scale, -mk));
+      if (e > 0.f) u = fmaf(e, y, u);
+    }
+    __syncthreads();  // everyone has read the first reduction's entries
+    const float uw = warp_sum(u);
+    if (lane == 0) red[warp] = uw;
+    __syncthreads();
+    const float tot = warp_sum(lane < NW ? red[lane] : 0.f);
+    if (ENT == 1) st.U = tot;
+    if (ENT == 2) st.U2 = tot;
+  }
   return st;
 }
 
@@ -272,14 +299,20 @@ __device__ __forceinline__ float chosen_logit(const KernelParams& p, int64_t n, 
 // Second streaming pass over one row: dlogits = g*(softmax - onehot) (times dy/dx with the soft-cap)
 // in bf16.  g == 0 writes exact zeros without reading the logits.
 // LDSRC: load flavour of the source row when it differs from the store flavour LD (3 = shared memory).
-template <int THREADS, int UNROLL, bool CAP, int LD, int LDSRC = -1>
+// ENTG adds cot * dH/dlogits, H the entropy of softmax(y/temperature):
+//   dH/dy_j = -(1/temp) * q_j * ((y_j/temp - lse2) + H),  q = softmax(y/temp), lse2 = log-sum-exp of y/temp.
+struct EntropyGrad {
+  float cot, H, lse2, inv_temp;
+};
+template <int THREADS, int UNROLL, bool CAP, int LD, int LDSRC = -1, bool ENTG = false>
 __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, int64_t V, float g, float lse,
-                                          int64_t cl, const SoftCap& sc, uint64_t pol) {
+                                          int64_t cl, const SoftCap& sc, uint64_t pol,
+                                          const EntropyGrad eg = EntropyGrad{0.f, 0.f, 0.f, 1.f}) {
   const int tid = threadIdx.x;
   const RowSplit sp(d16, V);  // the caller guarantees logits and dlogits rows share alignment
   uint4* dvec = reinterpret_cast<uint4*>(d16 + sp.head);
 
-  if (g == 0.f) {
+  if (g == 0.f && (!ENTG || eg.cot == 0.f)) {
     // Unscored row, masked token or zero advantage: exact zeros, logits are not read.
     if (tid < sp.head) d16[tid] = 0;
     if (tid < sp.tail) d16[sp.head + (sp.nvec << 3) + tid] = 0;
@@ -294,7 +327,15 @@ __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, in
 
   auto one = [&](float x, int64_t j) -> float {  // scalar path: signed f32 result
     float d;
-    if (CAP) {
+    if (ENTG) {
+      const float y = CAP ? sc.y(x) : x;
+      d = g * ex2f((y - lse) * kLog2e);
+      if (j == cl) d -= g;
+      const float z = fmaf(y, eg.inv_temp, -eg.lse2);
+      const float q = ex2f(z * kLog2e);
+      if (q > 0.f) d -= eg.cot * eg.inv_temp * q * (z + eg.H);
+      if (CAP) d *= sc.dydx(y);
+    } else if (CAP) {
       const float y = sc.y(x);
       d = ex2f(fmaf(y, kLog2e, off));
       d = g < 0.f ? -d : d;
@@ -326,12 +367,12 @@ __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, in
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
     uint32_t o[4];
     bool near = false;
-    if (CAP && idx != cv) {
+    if (CAP && !ENTG && idx != cv) {
       const uint32_t mx2 = bf16x2_max(bf16x2_max(w[0], w[1]), bf16x2_max(w[2], w[3]));
       const uint32_t mn2 = bf16x2_min(bf16x2_min(w[0], w[1]), bf16x2_min(w[2], w[3]));
       near = fminf(bf16lo(mn2), bf16hi(mn2)) >= -sc.cap && fmaxf(bf16lo(mx2), bf16hi(mx2)) <= sc.cap;
     }
-    if (!CAP && idx != cv) {
+    if (!CAP && !ENTG && idx != cv) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float a = ex2f(fmaf(bf16lo(w[j]), kLog2e, off));

@@ -42,6 +42,7 @@ __global__ void __launch_bounds__(THREADS) row_stats_kernel(const KernelParams p
       const float lse = st.M + logf(st.S);
       p.per_token_logps[n] = (yc - lse) * inv_temp;
       if (p.lse) p.lse[n] = lse;
+      if (p.lse_scaled) p.lse_scaled[n] = scaled_lse<ENT>(p, st, lse);
       if (ENT != 0 && p.token_entropy) {
         p.token_entropy[n] = (ENT == 1) ? lse - st.U / st.S
                                         : st.M * inv_temp + logf(st.S2) - inv_temp * st.U2 / st.S2;
@@ -51,6 +52,7 @@ __global__ void __launch_bounds__(THREADS) row_stats_kernel(const KernelParams p
       p.per_token_logps[n] = o.lp;
       if (ENT != 0 && p.token_entropy) p.token_entropy[n] = o.entropy;
       p.lse[n] = o.lse;
+      if (p.lse_scaled) p.lse_scaled[n] = scaled_lse<ENT>(p, st, o.lse);
       p.grad_coef[n] = o.grad_coef;
       p.loss_terms[n] = o.loss_term;
     }
@@ -85,6 +87,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const KernelParams p) {
   p.per_token_logps[n] = o.lp;
   if (ENT != 0 && p.token_entropy) p.token_entropy[n] = o.entropy;
   p.lse[n] = o.lse;
+  if (p.lse_scaled) p.lse_scaled[n] = scaled_lse<ENT>(p, st, o.lse);
   p.grad_coef[n] = o.grad_coef;
   p.loss_terms[n] = o.loss_term;
 }
@@ -107,8 +110,9 @@ __global__ void __launch_bounds__(1024) loss_reduce_kernel(const KernelParams p)
   }
 }
 
-// Backward sweep.  One CTA per logits row (scored or not).
-template <int THREADS, int UNROLL, bool CAP>
+// Backward sweep.  One CTA per logits row (scored or not).  ENTG: the cotangent of the token entropies
+// is folded in as well (the -entropy_coef * entropy term of plugins/training/ppo/module.py:140).
+template <int THREADS, int UNROLL, bool CAP, bool ENTG>
 __global__ void __launch_bounds__(THREADS) dlogits_kernel(const KernelParams p) {
   const int64_t r = blockIdx.x;  // row index over n_seqs*seq_rows
   const int64_t b = r / p.seq_rows;
@@ -117,6 +121,7 @@ __global__ void __launch_bounds__(THREADS) dlogits_kernel(const KernelParams p) 
   uint16_t* d16 = reinterpret_cast<uint16_t*>(p.dlogits + r * p.row_stride);
   float g = 0.f, lse = 0.f;
   int64_t cl = -1;
+  EntropyGrad eg{0.f, 0.f, 0.f, 1.f};
   if (t < p.scored_rows) {
     const int64_t n = b * p.scored_rows + t;
     const float nv = p.total_valid_dev ? *p.total_valid_dev : p.total_valid;
@@ -126,9 +131,15 @@ __global__ void __launch_bounds__(THREADS) dlogits_kernel(const KernelParams p) 
     int64_t c = p.chosen_ids[n];
     c = c < 0 ? 0 : (c >= p.vocab_total ? p.vocab_total - 1 : c);
     cl = c - p.vocab_start;
+    if (ENTG) {
+      eg.cot = p.entropy_cotangent[n];  // a cotangent of its own: grad_scale belongs to the loss
+      eg.H = p.token_entropy[n];
+      eg.lse2 = p.lse_scaled ? p.lse_scaled[n] : lse;
+      eg.inv_temp = p.inv_temperature;
+    }
   }
   const SoftCap sc(CAP ? p.softcap : 1.0f);
-  row_pass2<THREADS, UNROLL, CAP, 1>(x16, d16, p.vocab, g, lse, cl, sc, 0);
+  row_pass2<THREADS, UNROLL, CAP, 1, -1, ENTG>(x16, d16, p.vocab, g, lse, cl, sc, 0, eg);
 }
 
 // Any-alignment fallback for the rare case where logits and dlogits rows do not share
@@ -247,10 +258,15 @@ cudaError_t launch_dlogits(const KernelParams& p, cudaStream_t s) {
       dlogits_scalar_kernel<true><<<static_cast<unsigned>(R), 256, 0, s>>>(p);
     else
       dlogits_scalar_kernel<false><<<static_cast<unsigned>(R), 256, 0, s>>>(p);
+  } else if (p.entropy_cotangent) {
+    if (cap)
+      dlogits_kernel<kBwdThreads, kBwdUnroll, true, true><<<static_cast<unsigned>(R), kBwdThreads, 0, s>>>(p);
+    else
+      dlogits_kernel<kBwdThreads, kBwdUnroll, false, true><<<static_cast<unsigned>(R), kBwdThreads, 0, s>>>(p);
   } else if (cap) {
-    dlogits_kernel<kBwdThreads, kBwdUnroll, true><<<static_cast<unsigned>(R), kBwdThreads, 0, s>>>(p);
+    dlogits_kernel<kBwdThreads, kBwdUnroll, true, false><<<static_cast<unsigned>(R), kBwdThreads, 0, s>>>(p);
   } else {
-    dlogits_kernel<kBwdThreads, kBwdUnroll, false><<<static_cast<unsigned>(R), kBwdThreads, 0, s>>>(p);
+    dlogits_kernel<kBwdThreads, kBwdUnroll, false, false><<<static_cast<unsigned>(R), kBwdThreads, 0, s>>>(p);
   }
   count_launch();
   return cudaGetLastError();

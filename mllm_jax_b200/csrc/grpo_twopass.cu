@@ -18,10 +18,12 @@
 //            write-only
 // While a CTA waits for peers the other resident CTAs of the SM keep streaming.  Ranks walk the rows
 // in the same order and a CTA only waits for the row it owns, so the lowest unfinished row on every
-// GPU can always make progress; waits are bounded by wall-clock time (then a status bit is raised
-// and the CTA carries on).  Exchange buffers are double-buffered by the parity of the epoch: a rank
-// can start call e+2 only after every peer has published all of call e+1, i.e. finished call e.
-#include <cstdlib>
+// GPU can always make progress.  Waits are bounded by wall-clock time; a row that gives up raises a
+// status bit, is poisoned (log-prob and loss term NaN, zero gradient) and makes every later wait of
+// the call return after one look, so a dead peer costs one wait limit per call, not one per row.
+// Exchange buffers are double-buffered by the parity of the epoch: a rank can start call e+2 only
+// after every peer has published all of call e+1, i.e. finished call e.
+#include <atomic>
 
 #include "grpo_cluster.cuh"
 #include "grpo_common.cuh"
@@ -30,7 +32,15 @@
 
 namespace grpo {
 
-constexpr unsigned long long kPeerWaitLimitNs = 2000000000ull;  // 2 s
+// Forced plan of the tuning / test hook (mllm_grpo_set_plan_override); 0 (-1 for staged) = automatic.
+static std::atomic<int> g_force_cluster{0}, g_force_threads{0}, g_force_batch{0}, g_force_staged{-1};
+void set_two_pass_override(int cluster, int threads, int load_batch, int staged) {
+  g_force_cluster = cluster;
+  g_force_threads = threads;
+  g_force_batch = load_batch;
+  g_force_staged = staged;
+}
+
 
 // One exchanged word: value bits in the low half, the epoch in the high half.
 __device__ __forceinline__ unsigned long long make_word(float v, int epoch) {
@@ -71,6 +81,7 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
   extern __shared__ __align__(128) unsigned char slice_smem[];
   __shared__ unsigned long long load_bar;
   __shared__ int abort_flag;
+  __shared__ int peer_lost;  // SHARDED: a wait for another rank's partial of this row ran out
   __shared__ float red[160];
   __shared__ float bc[2];
   __shared__ __align__(16) float4 slots[8];  // cluster slices' partials
@@ -96,6 +107,7 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
   }
   // Tell the cluster peers this CTA is running (its shared memory exists) without blocking yet.
   if (CL > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  if (SHARDED && tid == 0) peer_lost = 0;  // ordered before its writers by the barrier inside the first pass
   if (SMEM && tid == 0) {
     abort_flag = 0;
     const uint32_t bar = cl::smem_u32(&load_bar);
@@ -156,15 +168,22 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
       const uint32_t want = static_cast<uint32_t>(p.exchange_epoch);
       unsigned long long w0, w1, w2, w3;
       unsigned long long t0 = 0;
-      for (;;) {
+      const volatile int32_t* status = p.device_status;
+      for (int spin = 0;; ++spin) {
         ld_words2_sys(src, w0, w1);
         ld_words2_sys(src + 2, w2, w3);
         if (static_cast<uint32_t>(w0 >> 32) == want && static_cast<uint32_t>(w1 >> 32) == want &&
             static_cast<uint32_t>(w2 >> 32) == want && static_cast<uint32_t>(w3 >> 32) == want)
           break;
+        // Some wait of this call (or an uncleared earlier one) already ran out: do not wait again.
+        if ((spin & 63) == 0 && (*status & MLLM_GRPO_DEV_WAIT_TIMEOUT)) {
+          peer_lost = 1;
+          break;
+        }
         if (t0 == 0) t0 = cl::globaltimer();
-        if (cl::globaltimer() - t0 > kPeerWaitLimitNs) {
-          if (p.device_status) atomicOr(p.device_status, MLLM_GRPO_DEV_WAIT_TIMEOUT);
+        if (cl::globaltimer() - t0 > p.peer_wait_ns) {
+          atomicOr(p.device_status, MLLM_GRPO_DEV_WAIT_TIMEOUT);
+          peer_lost = 1;
           break;
         }
         __nanosleep(32);
@@ -183,11 +202,16 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
     all.U = m.z;
     all.S2 = st.S2;  // temperature != 1 entropy exists only unsplit (CL == 1, not sharded)
     all.U2 = st.U2;
-    const TokenOut o = token_epilogue<ENT>(p, n, b, all, m.w);
+    TokenOut o = token_epilogue<ENT>(p, n, b, all, m.w);
+    if (SHARDED && peer_lost) {  // merged stale words: make the row unusable instead of silently wrong
+      o.lp = o.entropy = o.loss_term = __int_as_float(0x7fc00000);
+      o.grad_coef = 0.f;
+    }
     if (rank == 0) {
       p.per_token_logps[n] = o.lp;
       if (ENT != 0 && p.token_entropy) p.token_entropy[n] = o.entropy;
       p.lse[n] = o.lse;
+      if (p.lse_scaled) p.lse_scaled[n] = scaled_lse<ENT>(p, all, o.lse);
       p.grad_coef[n] = o.grad_coef;
       p.loss_terms[n] = o.loss_term;
     }
@@ -220,7 +244,9 @@ cudaError_t launch_k(const KernelParams& p, bool smem, cudaStream_t s) {
   }
   const size_t dyn = smem ? slice_bytes : 0;
   cudaError_t e;
-  if (smem && dyn > 48 * 1024) {
+  // The 48 KB a launch gets without opting in covers static + dynamic shared memory, and the kernel
+  // has about 1 KB of static: opt in from 44 KB of row on.
+  if (smem && dyn > 44 * 1024) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     if (e != cudaSuccess) return e;
   }
@@ -312,27 +338,25 @@ void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, i
   if (sharded) cl = 1;
   const bool aligned16 = !(p.vocab & 7) && !(p.row_stride & 7) && !(reinterpret_cast<uintptr_t>(p.logits) & 15) &&
                          !(reinterpret_cast<uintptr_t>(p.dlogits) & 15);
-  const char* env_cl = std::getenv("MLLM_GRPO_L2_CLUSTER");
-  if (env_cl) cl = std::atoi(env_cl);
+  const int f_cl = g_force_cluster.load(std::memory_order_relaxed), f_th = g_force_threads.load(std::memory_order_relaxed);
+  const int f_un = g_force_batch.load(std::memory_order_relaxed), f_sm = g_force_staged.load(std::memory_order_relaxed);
+  if (f_cl > 0) cl = f_cl;
   if (cl != 1 && cl != 2 && cl != 4 && cl != 8) cl = 1;
   const int64_t nvec = p.vocab / 8;
   if (cl > 1) {
     const int64_t per = (nvec + cl - 1) / cl;
     if (!aligned16 || ent == 2 || nvec - (cl - 1) * per <= 0 || p.n_seqs * p.seq_rows * cl >= (int64_t(1) << 31)) cl = 1;
   }
-  const char* env_th = std::getenv("MLLM_GRPO_L2_THREADS");
   // measured on one B200 (unsplit rows): 38 KB rows 64 threads, 76 KB 256, 152 KB and longer 512
-  int th = env_th ? std::atoi(env_th) : (cl > 1 ? 128 : (row_bytes < 56 * 1024 ? 64 : (row_bytes < 112 * 1024 || sharded ? 256 : 512)));
+  int th = f_th > 0 ? f_th : (cl > 1 ? 128 : (row_bytes < 56 * 1024 ? 64 : (row_bytes < 112 * 1024 || sharded ? 256 : 512)));
   // Rows of at most 48 KB that are not split: stage the row in shared memory with one bulk (TMA) copy
   // and run both passes from there (38 KB rows on one B200: 0.400 ms against 0.452 ms through
   // registers).  Longer rows and cluster slices measured slower that way (too few CTAs per SM).
   const size_t slice_bytes = size_t(cl > 1 ? (nvec + cl - 1) / cl : nvec) * 16;
   bool sm = cl == 1 && aligned16 && ent != 2 && slice_bytes <= 48 * 1024 && slice_bytes >= 4096;
-  const char* env_sm = std::getenv("MLLM_GRPO_SMEM");
-  if (env_sm) sm = std::atoi(env_sm) != 0 && cl == 1 && aligned16 && ent != 2 && slice_bytes <= 100 * 1024;
-  if (sm && !env_th) th = 256;
-  const char* env_un = std::getenv("MLLM_GRPO_L2_UNROLL");
-  if (env_un) un = std::atoi(env_un);
+  if (f_sm >= 0) sm = f_sm != 0 && cl == 1 && aligned16 && ent != 2 && slice_bytes <= 99 * 1024;
+  if (sm && f_th <= 0) th = 256;
+  if (f_un > 0) un = f_un;
   *cluster = cl;
   *threads = th;
   *smem = sm;

@@ -129,6 +129,9 @@ class TokenLossProblem:
         self.shard_rank = 0
         self.peer_ptrs = None      # device addresses of every rank's exchange buffer (fused sharded path)
         self.exchange_epoch = 0
+        self.peer_wait_ms = 0      # 0 = the library's default (2000 ms)
+        self.lse_scaled: Optional[torch.Tensor] = None         # residual of the entropy gradient (temperature != 1)
+        self.entropy_cotangent: Optional[torch.Tensor] = None  # [B, T] cotangent of token_entropy for mllm_grpo_bwd
 
     def args(self) -> GrpoArgs:
         a = GrpoArgs()
@@ -159,7 +162,8 @@ class TokenLossProblem:
         a.dlogits = _ptr(self.dlogits)
         a.partials, a.gathered_partials, a.n_shards = _ptr(self.partials), _ptr(self.gathered), self.n_shards
         a.device_status = _ptr(self.device_status)
-        a.shard_rank, a.exchange_epoch = self.shard_rank, self.exchange_epoch
+        a.shard_rank, a.exchange_epoch, a.peer_wait_ms = self.shard_rank, self.exchange_epoch, int(self.peer_wait_ms)
+        a.lse_scaled, a.entropy_cotangent = _ptr(self.lse_scaled), _ptr(self.entropy_cotangent)
         if self.peer_ptrs is not None:
             for q, ptr in enumerate(self.peer_ptrs):
                 a.peer_exchange[q] = ptr
@@ -191,8 +195,15 @@ class _GrpoLoss(torch.autograd.Function):
     backward receives the scalar cotangent of the loss and streams the logits once more."""
 
     @staticmethod
-    def forward(ctx, logits, prob: TokenLossProblem, inplace_backward: bool, eager_grad: bool = False):
+    def forward(ctx, logits, prob: TokenLossProblem, inplace_backward: bool, eager_grad: bool = False,
+                entropy_grad: bool = False):
         ctx.eager = bool(eager_grad) and logits.requires_grad
+        ctx.entropy_grad = bool(entropy_grad) and prob.token_entropy is not None
+        if ctx.entropy_grad:
+            if ctx.eager:
+                raise ValueError("the entropy's cotangent is only known in backward(): eager_grad cannot serve it")
+            if prob.cfg.temperature != 1.0:
+                prob.lse_scaled = torch.empty_like(prob.lse)
         if ctx.eager:
             # forward and gradient in one kernel (cotangent 1); backward applies a late cotangent, if any
             prob.grad_scale = 1.0
@@ -204,19 +215,28 @@ class _GrpoLoss(torch.autograd.Function):
         ctx.inplace = inplace_backward
         ctx.mark_non_differentiable(prob.per_token_logps)
         ent = prob.token_entropy if prob.token_entropy is not None else prob.per_token_logps.new_empty(0)
-        ctx.mark_non_differentiable(ent)
+        if not ctx.entropy_grad:
+            ctx.mark_non_differentiable(ent)
         return prob.loss.reshape(()), prob.per_token_logps, ent
 
     @staticmethod
-    def backward(ctx, grad_loss, _g_lp, _g_ent):
+    def backward(ctx, grad_loss, _g_lp, g_ent):
         prob: TokenLossProblem = ctx.prob
+        if grad_loss is None:  # only the entropy output was used
+            grad_loss = prob.loss.new_zeros(())
         prob.grad_scale_dev = grad_loss.to(torch.float32).reshape(1).contiguous()
         if ctx.eager:
             prob.run("mllm_grpo_scale_grad")  # returns at once on the device when the cotangent is 1
-            return prob.dlogits, None, None, None
+            return prob.dlogits, None, None, None, None
         prob.alloc_dlogits(ctx.inplace)
-        prob.run("mllm_grpo_bwd")
-        return prob.dlogits, None, None, None
+        if ctx.entropy_grad and g_ent is not None:
+            # dlogits = grad_loss * grad_coef/Nv * (softmax - onehot) + g_ent * dH/dlogits in one sweep
+            prob.entropy_cotangent = g_ent.to(torch.float32).contiguous()
+            prob.run("mllm_grpo_bwd")
+            prob.entropy_cotangent = None
+        else:
+            prob.run("mllm_grpo_bwd")
+        return prob.dlogits, None, None, None, None
 
 
 def _shifted_side(input_ids: torch.Tensor, labels: torch.Tensor):
@@ -229,8 +249,12 @@ def grpo_token_loss(logits: torch.Tensor, input_ids: torch.Tensor, labels: torch
                     ref_per_token_logps: Optional[torch.Tensor] = None, *, temperature: float = 1.0,
                     epsilon_low: float = 0.2, epsilon_high: float = 0.3, beta: float = 0.0,
                     softcap: Optional[float] = None, compute_entropy: bool = True,
-                    inplace_backward: bool = False, eager_grad: bool = False) -> dict:
+                    inplace_backward: bool = False, eager_grad: bool = False, entropy_grad: bool = False) -> dict:
     """GRPO token loss on the reference layout.
+
+    entropy_grad=True makes the returned token_entropy differentiable with respect to the logits as well
+    (the -entropy_coef * entropy term of plugins/training/ppo/module.py:140): backward() then adds
+    cotangent * dH/dlogits inside the same streaming sweep.
 
     eager_grad=True computes dlogits together with the loss in one kernel (logits cross HBM once)
     and lets backward() merely hand them over; a cotangent other than 1 is applied by one extra
@@ -246,7 +270,7 @@ def grpo_token_loss(logits: torch.Tensor, input_ids: torch.Tensor, labels: torch
     ids, mask = _shifted_side(input_ids, labels)
     prob = TokenLossProblem(logits, ids, mask, advantages, total_valid_token_count, old_per_token_logps,
                             ref_per_token_logps, cfg, scored_rows=logits.shape[1] - 1)
-    loss, lp, ent = _GrpoLoss.apply(logits, prob, inplace_backward, eager_grad)
+    loss, lp, ent = _GrpoLoss.apply(logits, prob, inplace_backward, eager_grad, entropy_grad)
     return {"loss": loss, "per_token_logps": lp, "token_entropy": ent if compute_entropy else None}
 
 

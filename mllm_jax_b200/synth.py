@@ -53,7 +53,8 @@ CONFIGS = {
 def sweep_workload(n_tokens: int) -> Workload:
     """Token-count sweep at V=151936: one 'sequence' per 1024 tokens, half the tokens valid."""
     seq = 1024 if n_tokens % 1024 == 0 else n_tokens
-    return Workload(f"cfg4-sweep-{n_tokens}", n_tokens // seq, seq, 151936, half_valid_runs=True)
+    return Workload(f"cfg4-sweep-{n_tokens}", n_tokens // seq, seq, 151936, half_valid_runs=True,
+                    group=min(8, n_tokens // seq))
 
 
 def scaled(w: Workload, **kw) -> Workload:
@@ -83,29 +84,47 @@ def exact_logprobs(logits: torch.Tensor, ids: torch.Tensor, softcap: Optional[fl
     return out.reshape(ids.shape)
 
 
+BLOCK_ROWS = 1024  # logits are generated in blocks of this many rows, each block from its own seed
+
+
+def parse_workload(name: str) -> Workload:
+    """cfg0..cfg3, or cfg4-<tokens> for one point of the token-count sweep (e.g. cfg4-65536, cfg4-1048576)."""
+    if name in CONFIGS:
+        return CONFIGS[name]
+    if name.startswith("cfg4-"):
+        return sweep_workload(int(name[5:]))
+    raise ValueError(f"unknown workload {name!r}: expected one of {sorted(CONFIGS)} or cfg4-<tokens>")
+
+
 def make_inputs(w: Workload, seed: int = 0, device: str = "cpu", vocab_shard: Optional[tuple] = None,
-                logits_chunk_rows: int = 2048) -> dict:
+                row_shard: Optional[tuple] = None, want_logits: bool = True) -> dict:
     """Build one batch.  Returns logits [B, T, V] bf16, token_ids / mask / old / ref [B, T],
-    advantages [B], total_valid (float).  With vocab_shard=(rank, k) only columns
-    [rank*V/k, (rank+1)*V/k) of the logits are materialised (same values as the full tensor
-    would hold is NOT guaranteed; old/ref then derive from noise alone and are still seeded)."""
+    advantages [B], total_valid (float, over the WHOLE batch).
+
+    The logits are generated block by block (BLOCK_ROWS rows of the flattened [B*T, V] tensor), block i
+    from a generator seeded by (seed, i), always at full width.  So every shard is a slice of one and the
+    same tensor, whatever the number of ranks:
+      vocab_shard=(rank, k): only columns [rank*V/k, (rank+1)*V/k) are kept (side arrays whole);
+      row_shard=(rank, k):   only sequences [rank*B/k, (rank+1)*B/k) are generated and returned
+                             (side arrays sliced to them; total_valid stays global).
+    old / ref log-probs are the exact log-probs of the full rows plus seeded noise in either case.
+    (Blocks are bit-identical across shardings on one kind of device; CPU and CUDA generators differ.)"""
     dev = torch.device(device)
-    g = torch.Generator(device=dev)
-    g.manual_seed(1000003 * seed + 17)
     B, T, V = w.n_seqs, w.seq_len, w.vocab
-    cols = V
+    c0, c1 = 0, V
     if vocab_shard is not None:
         rank, k = vocab_shard
         if V % k:
             raise ValueError(f"vocab {V} does not split over {k} shards")
-        cols = V // k
-        g.manual_seed(1000003 * seed + 17 + 7919 * (rank + 1))
-    logits = torch.empty(B, T, cols, dtype=torch.bfloat16, device=dev)
-    flat = logits.view(B * T, cols)
-    for s in range(0, B * T, logits_chunk_rows):
-        n = min(logits_chunk_rows, B * T - s)
-        flat[s:s + n] = (torch.randn(n, cols, generator=g, device=dev, dtype=torch.float32) * w.sigma).to(torch.bfloat16)
+        c0, c1 = rank * (V // k), (rank + 1) * (V // k)
+    b0, b1 = 0, B
+    if row_shard is not None:
+        rank, k = row_shard
+        if B % k:
+            raise ValueError(f"{B} sequences do not split over {k} ranks")
+        b0, b1 = rank * (B // k), (rank + 1) * (B // k)
 
+    # side arrays of the whole batch (tiny), from one CPU generator
     gs = torch.Generator(device="cpu")
     gs.manual_seed(7 * seed + 3)
     ids = torch.randint(0, V, (B, T), generator=gs, dtype=torch.int64).to(torch.int32)
@@ -126,13 +145,29 @@ def make_inputs(w: Workload, seed: int = 0, device: str = "cpu", vocab_shard: Op
         mask = (torch.arange(T)[None, :] < lens[:, None]).float()
     noise_old = torch.randn(B, T, generator=gs) * w.old_noise
     noise_ref = torch.randn(B, T, generator=gs) * w.ref_noise
-    ids, adv, mask = ids.to(dev), adv.to(dev), mask.to(dev)
-    if vocab_shard is None:
-        lp = exact_logprobs(logits, ids, w.softcap)
-    else:
-        lp = torch.full((B, T), -12.0, device=dev)  # placeholder centre; the shards never see full rows
+    total_valid = float(mask.sum().item())
+
+    r0, r1 = b0 * T, b1 * T  # rows of the flattened tensor this call materialises
+    logits = torch.empty(b1 - b0, T, c1 - c0, dtype=torch.bfloat16, device=dev) if want_logits else None
+    flat = logits.view(r1 - r0, c1 - c0) if want_logits else None
+    lp = torch.empty(r1 - r0, dtype=torch.float32, device=dev)
+    ids_dev = ids.to(dev).reshape(-1)
+    g = torch.Generator(device=dev)
+    for blk in range(r0 // BLOCK_ROWS, (r1 + BLOCK_ROWS - 1) // BLOCK_ROWS):
+        s, e = blk * BLOCK_ROWS, min((blk + 1) * BLOCK_ROWS, B * T)
+        g.manual_seed(1000003 * seed + 17 + 7919 * blk)
+        x = (torch.randn(e - s, V, generator=g, device=dev, dtype=torch.float32) * w.sigma).to(torch.bfloat16)
+        lo, hi = max(s, r0), min(e, r1)
+        x = x[lo - s:hi - s]
+        lp[lo - r0:hi - r0] = exact_logprobs(x, ids_dev[lo:hi], w.softcap)
+        if want_logits:
+            flat[lo - r0:hi - r0] = x[:, c0:c1]
+        del x
+
+    sl = slice(b0, b1)
+    lp = lp.view(b1 - b0, T)
     return {
-        "logits": logits, "token_ids": ids, "mask": mask, "advantages": adv,
-        "old_logps": lp + noise_old.to(dev), "ref_logps": lp + noise_ref.to(dev),
-        "total_valid": float(mask.sum().item()), "exact_logps": lp,
+        "logits": logits, "token_ids": ids[sl].to(dev), "mask": mask[sl].to(dev), "advantages": adv[sl].to(dev),
+        "old_logps": lp + noise_old[sl].to(dev), "ref_logps": lp + noise_ref[sl].to(dev),
+        "total_valid": total_valid, "exact_logps": lp,
     }

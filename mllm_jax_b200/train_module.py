@@ -61,9 +61,11 @@ class TrainGRPOModule:
     """Drop-in for the reference module: same fields (train_modules/__init__.py:85-94).
 
     `pad_token_id`, `num_pre_Q`, `max_lengths`, `entropy_threshold` are carried and unused, as in
-    the reference.  `ref_model`, when given with beta != 0, supplies the reference log-probs
-    of the k3 KL term (an extension: the reference computes them but drops the term, :129-132,191);
-    `inputs["ref_per_token_logps"]` may supply them directly instead.
+    the reference.  With the default `use_kl=False` the loss is the reference's: the clipped surrogate
+    alone, whatever `beta` and `ref_model` are (the reference computes the reference-policy log-probs but
+    drops the KL term, :129-132, :176-180, :191, so they are not computed here at all).
+    `use_kl=True` is an extension: beta * k3 KL against the reference policy is added to the loss and its
+    gradient, with the log-probs taken from `inputs["ref_per_token_logps"]` or from `ref_model`.
     """
 
     model: Any
@@ -78,6 +80,7 @@ class TrainGRPOModule:
     entropy_threshold: float = 0.3
     softcap: Optional[float] = None
     eager_grad: bool = True  # loss and dlogits from one kernel; backward() applies a late cotangent if any
+    use_kl: bool = False     # extension, off by default: add beta * k3 KL to the reference policy
 
     def __call__(self, inputs: Mapping[str, Any]) -> dict:
         from .ops import token_logprobs
@@ -87,8 +90,8 @@ class TrainGRPOModule:
         labels = inputs["labels"]
         logits, _ = self.model(input_ids=input_ids, attention_mask=attention_mask)
 
-        ref_lp = inputs.get("ref_per_token_logps")
-        if ref_lp is None and self.beta != 0 and self.ref_model is not None:
+        ref_lp = inputs.get("ref_per_token_logps") if self.use_kl else None
+        if self.use_kl and ref_lp is None and self.beta != 0 and self.ref_model is not None:
             with torch.no_grad():
                 ref_logits, _ = self.ref_model(input_ids=input_ids, attention_mask=attention_mask)
             # reference-policy log-probs are not divided by the temperature (:130-132)
@@ -112,7 +115,7 @@ class TrainGRPOModule:
 
 
 def ppo_policy_terms(logits: torch.Tensor, inputs: Mapping[str, Any], *, temperature: float = 1.0,
-                     epsilon_low: float = 0.2, epsilon_high: float = 0.2) -> dict:
+                     epsilon_low: float = 0.2, epsilon_high: float = 0.2, entropy_grad: bool = False) -> dict:
     """Policy loss, global entropy and log-probs as PPOActorCriticModule computes them
     (plugins/training/ppo/module.py:66-102): advantages [B], [B, 1] or [B, L-1]; entropy is one
     masked mean over the batch with a 1e-8 guard (:77).  The value-loss tail (:104-140) is
@@ -122,7 +125,7 @@ def ppo_policy_terms(logits: torch.Tensor, inputs: Mapping[str, Any], *, tempera
         logits, inputs["input_ids"], labels, inputs["advantages"],
         total_valid_token_count=inputs.get("total_valid_token_count"),
         old_per_token_logps=inputs.get("old_per_token_logps"),
-        temperature=temperature, epsilon_low=epsilon_low, epsilon_high=epsilon_high,
+        temperature=temperature, epsilon_low=epsilon_low, epsilon_high=epsilon_high, entropy_grad=entropy_grad,
     )
     m = labels[:, 1:].to(torch.float32)
     entropy = (out["token_entropy"] * m).sum() / (m.sum() + 1e-8)
@@ -225,14 +228,15 @@ def ppo_actor_critic_terms(logits: torch.Tensor, values: torch.Tensor, inputs: M
                            entropy_coef: float = 0.0) -> dict:
     """The return dict of PPOActorCriticModule.__call__ (plugins/training/ppo/module.py:142-150) from
     the lm_head's logits [B, L, V] and the value head's values [B, L]; `loss` is differentiable with
-    respect to both.  A non-zero entropy_coef (:140; 0.0 in every configuration the reference ships)
-    needs the gradient of the entropy with respect to the logits, which the kernels do not produce."""
-    if float(entropy_coef) != 0.0:
-        raise NotImplementedError("entropy_coef != 0 needs d entropy / d logits, which is not implemented")
+    respect to both.  A non-zero entropy_coef (:140; 0.0 in every configuration the reference ships) makes
+    the entropy differentiable too: its cotangent per token rides along in the backward sweep of the logits."""
+    want_entropy_grad = float(entropy_coef) != 0.0
     pol = ppo_policy_terms(logits, inputs, temperature=temperature, epsilon_low=epsilon_low,
-                           epsilon_high=epsilon_high)
+                           epsilon_high=epsilon_high, entropy_grad=want_entropy_grad)
     value_loss, value_pred_mean, return_mean = _ValueLoss.apply(values, inputs, value_clip_range)
     loss = pol["policy_loss"] + float(value_coef) * value_loss                                     # :140
+    if want_entropy_grad:
+        loss = loss - float(entropy_coef) * pol["entropy"]
     return {"loss": loss, "policy_loss": pol["policy_loss"], "value_loss": value_loss, "entropy": pol["entropy"],
             "value_pred_mean": value_pred_mean, "return_mean": return_mean,
             "per_token_logps": pol["per_token_logps"]}

@@ -129,7 +129,8 @@ class VocabParallelLoss:
                 "dlogits": d, "problem": p}
 
     def plan_fused(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None, ref_logps=None,
-                   dlogits=None, grad_scale: float = 1.0, scored_rows: Optional[int] = None) -> TokenLossProblem:
+                   dlogits=None, grad_scale: float = 1.0, scored_rows: Optional[int] = None,
+                   peer_wait_ms: int = 0) -> TokenLossProblem:
         """Bind buffers once for repeated fused steps on the same addresses (static shapes, new
         contents each step): `step_fused(plan)` then only bumps the epoch and launches.
         scored_rows = L - 1 takes the reference layout (row i scored against token i + 1, side arrays [B, L-1])."""
@@ -138,6 +139,7 @@ class VocabParallelLoss:
             self._peer = PeerExchange(p.N, shard_logits.device, self.group)
         p.peer_ptrs, p.shard_rank, p.n_shards = self._peer.ptrs, self.rank, self.world
         p.grad_scale = float(grad_scale)
+        p.peer_wait_ms = int(peer_wait_ms)  # tolerated skew between ranks; 0 = the library's 2000 ms
         if dlogits is not None:
             p.dlogits = dlogits
         else:
@@ -145,11 +147,25 @@ class VocabParallelLoss:
         return p
 
     def step_fused(self, p: TokenLossProblem) -> dict:
+        """One fused step on a plan.  The returned "device_status" is the int32 word the kernel ORs
+        MLLM_GRPO_DEV_* bits into: after a synchronisation, `raise_on_timeout(out)` (or a NaN loss) tells
+        that a peer did not show up within the wait limit and the step must be thrown away."""
         p.exchange_epoch = self._peer.next_epoch()
         p.run("mllm_grpo_fwd_bwd_sharded", reuse_args=p.exchange_epoch > 1 and getattr(p, "_planned", False))
         p._planned = True
         return {"loss": p.loss.reshape(()), "per_token_logps": p.per_token_logps, "token_entropy": p.token_entropy,
-                "dlogits": p.dlogits, "problem": p}
+                "dlogits": p.dlogits, "problem": p, "device_status": p.device_status}
+
+    @staticmethod
+    def raise_on_timeout(out: dict) -> None:
+        """Synchronising check of a fused step's status word; clears it so that the next step waits again."""
+        from . import _lib
+
+        status = int(out["device_status"].item())
+        if status & _lib.DEV_WAIT_TIMEOUT:
+            out["device_status"].zero_()
+            raise RuntimeError("vocabulary-parallel loss: a rank's partials did not arrive within the wait limit; "
+                               "the step's loss is NaN and its gradient must not be used")
 
     def value_and_grad_fused(self, shard_logits, token_ids, mask, advantages, total_valid, old_logps=None,
                              ref_logps=None, dlogits=None, grad_scale: float = 1.0,
@@ -172,11 +188,16 @@ class TokenParallelLoss:
         self.cfg = cfg or LossConfig()
 
     def value_and_grad(self, local_logits, token_ids, mask, advantages, total_valid_global, old_logps=None,
-                       ref_logps=None, dlogits=None, reduce_loss: bool = True) -> dict:
+                       ref_logps=None, dlogits=None, reduce_loss: bool = True, shifted: bool = False) -> dict:
+        """This rank's rows through mllm_grpo_fwd_bwd.  total_valid_global must be the count over ALL ranks'
+        rows; out["loss"] is then the global loss (sum of the ranks' shares) and out["local_loss"] this rank's
+        share.  shifted=True takes the reference layout (input_ids / labels [B, L])."""
         from .ops import grpo_value_and_grad
 
+        if total_valid_global is None:
+            raise ValueError("token-parallel ranks need the global total_valid_token_count")
         out = grpo_value_and_grad(local_logits, token_ids, mask, advantages, total_valid_global, old_logps, ref_logps,
-                                  cfg=self.cfg, dlogits=dlogits)
+                                  cfg=self.cfg, dlogits=dlogits, shifted=shifted)
         out["local_loss"] = out["loss"]
         if reduce_loss:
             out["loss"] = self.reduce_loss(out["loss"])

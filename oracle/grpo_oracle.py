@@ -125,8 +125,10 @@ def reference_value_and_grad(logits_bf16: torch.Tensor, inputs: Mapping[str, Any
 
 
 def ppo_policy_call(logits: torch.Tensor, inputs: Mapping[str, Any], *, temperature: float = 1.0,
-                    epsilon_low: float = 0.2, epsilon_high: float = 0.2, dtype=torch.float32) -> dict:
-    """Policy part of PPOActorCriticModule.__call__ (plugins/training/ppo/module.py:66-102)."""
+                    epsilon_low: float = 0.2, epsilon_high: float = 0.2, dtype=torch.float32,
+                    detach_entropy: bool = True) -> dict:
+    """Policy part of PPOActorCriticModule.__call__ (plugins/training/ppo/module.py:66-102).
+    detach_entropy=False keeps the entropy attached to the logits, for the -entropy_coef * entropy term of :140."""
     logits = logits.to(dtype)
     input_ids = inputs["input_ids"].long()
     chosen_ids = input_ids[:, 1:]                                             # :66
@@ -154,7 +156,8 @@ def ppo_policy_call(logits: torch.Tensor, inputs: Mapping[str, Any], *, temperat
     tv = inputs.get("total_valid_token_count")
     total_valid_token_count = mask_loss.sum() if tv is None else tv           # :101
     policy_loss = (per_token_loss * mask_loss).sum() / total_valid_token_count  # :102
-    return {"policy_loss": policy_loss, "entropy": entropy.detach(), "per_token_logps": per_token_logps.detach()}
+    return {"policy_loss": policy_loss, "entropy": entropy.detach() if detach_entropy else entropy,
+            "per_token_logps": per_token_logps.detach()}
 
 
 def ppo_value_call(values: torch.Tensor, inputs: Mapping[str, Any], *, value_clip_range: Optional[float] = 0.2,

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol(built_lib):
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/mllm_grpo.h but not exported"
     assert set(_lib.EXPORTS) <= set(names)
-    assert lib.mllm_grpo_abi_version() == 2
+    assert lib.mllm_grpo_abi_version() == 3
 
 
 def test_ctypes_struct_matches_c_layout(tmp_path):

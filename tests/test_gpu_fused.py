@@ -1,36 +1,20 @@
-"""The single-kernel implementations behind mllm_grpo_fwd_bwd.
+"""The implementations behind mllm_grpo_fwd_bwd.
 
-"auto" picks the two-pass kernel whose second read is served by L2 (rows split over a cluster
-when they are long); "cluster" is the row-resident kernel (distributed shared memory, TMA bulk
-copies in and out), taken only for 16-byte-aligned full rows; "sweeps" is the separate forward
-and backward kernels.  The tests force every mode, cluster size and thread count, check that a
-single-kernel path really ran (2 launches instead of 3), and compare with the CPU oracle under
-the usual gates."""
-import os
-
+The default is the two-pass kernel whose second read of a row is served on chip (L2, or shared memory
+for short unsplit rows; long rows are split over a thread-block cluster); the separate forward and
+backward kernels serve the rows it cannot take.  The tests force every cluster size, thread count,
+load-batch size and the staged form through the library's tuning hook, check that the single-kernel
+path really ran (2 launches instead of 3), and compare with the CPU oracle under the usual gates."""
 import pytest
 import torch
 
 import mllm_jax_b200 as G
+from mllm_jax_b200._lib import plan_override
 from oracle import grpo_oracle as O
 from tests.test_gpu_parity import check
 from tests.util import make_case, to_device
 
 pytestmark = pytest.mark.gpu
-
-ENV = ("MLLM_GRPO_FWD_BWD_MODE", "MLLM_GRPO_L2_CLUSTER", "MLLM_GRPO_L2_THREADS",
-       "MLLM_GRPO_FUSED_CLUSTER", "MLLM_GRPO_FUSED_THREADS", "MLLM_GRPO_FUSED_STAGES", "MLLM_GRPO_FUSED_CLUSTERS",
-       )
-
-
-@pytest.fixture(autouse=True)
-def clean_env():
-    saved = {k: os.environ.pop(k, None) for k in ENV}
-    yield
-    for k, v in saved.items():
-        os.environ.pop(k, None)
-        if v is not None:
-            os.environ[k] = v
 
 
 def run_fused(logits, inputs, cuda, expect_fused=True, inplace=False, compute_entropy=True, **attrs):
@@ -53,46 +37,26 @@ def run_fused(logits, inputs, cuda, expect_fused=True, inplace=False, compute_en
     return ref, got
 
 
-@pytest.mark.parametrize("cluster", [1, 2, 4, 8])
-@pytest.mark.parametrize("threads", [256, 512])
-def test_cluster_sizes(cuda, cluster, threads):
-    os.environ["MLLM_GRPO_FWD_BWD_MODE"] = "cluster"
-    os.environ["MLLM_GRPO_FUSED_CLUSTER"] = str(cluster)
-    os.environ["MLLM_GRPO_FUSED_THREADS"] = str(threads)
-    logits, inputs = make_case(5, 41, 32000, seed=50 + cluster, old="wide", ref=True)
-    ref, got = run_fused(logits, inputs, cuda, beta=0.04)
-    check(ref, got, f"cluster={cluster} threads={threads}")
-
-
-@pytest.mark.parametrize("mode", ["auto", "cluster"])
 @pytest.mark.parametrize("V", [64, 1024, 4104, 128256, 151936, 256000])
-def test_vocab_sizes_default_plan(cuda, V, mode):
-    os.environ["MLLM_GRPO_FWD_BWD_MODE"] = mode
+def test_vocab_sizes_default_plan(cuda, V):
     B, L = (2, 5) if V > 100000 else (3, 70)
     logits, inputs = make_case(B, L, V, seed=60, old="noisy", ref=True)
     ref, got = run_fused(logits, inputs, cuda, beta=0.04, epsilon_low=0.2, epsilon_high=0.2)
     check(ref, got, f"V={V}")
 
 
-@pytest.mark.parametrize("stages", [2, 3])
-@pytest.mark.parametrize("clusters", [1, 3, 0])
-def test_few_stages_and_few_clusters(cuda, stages, clusters):
-    """Long per-cluster row sequences (pipeline wrap-around of stages and exchange slots)."""
-    os.environ["MLLM_GRPO_FWD_BWD_MODE"] = "cluster"
-    os.environ["MLLM_GRPO_FUSED_CLUSTER"] = "2"
-    os.environ["MLLM_GRPO_FUSED_STAGES"] = str(stages)
-    if clusters:
-        os.environ["MLLM_GRPO_FUSED_CLUSTERS"] = str(clusters)
-    logits, inputs = make_case(3, 30, 2048, seed=61, old="wide", ref=True)
-    ref, got = run_fused(logits, inputs, cuda, beta=0.1)
-    check(ref, got, f"stages={stages} clusters={clusters}")
+@pytest.mark.parametrize("V", [22528, 24112, 24120, 24576])
+def test_staged_rows_up_to_the_48k_boundary(cuda, V):
+    """Unsplit rows of 44-48 KB are staged in shared memory; static + dynamic shared memory then exceeds
+    the 48 KB a launch gets without opting in, so the launcher has to raise the limit itself."""
+    logits, inputs = make_case(2, 7, V, seed=67, old="wide", ref=True)
+    ref, got = run_fused(logits, inputs, cuda, beta=0.04)
+    check(ref, got, f"V={V}")
 
 
-@pytest.mark.parametrize("mode", ["auto", "cluster"])
 @pytest.mark.parametrize("kind", ["no_old", "token_adv", "random_mask", "softcap", "no_entropy", "all_masked",
                                   "single_row"])
-def test_options_fused(cuda, kind, mode):
-    os.environ["MLLM_GRPO_FWD_BWD_MODE"] = mode
+def test_options_fused(cuda, kind):
     kw, attrs, extra = dict(old="noisy"), {}, {}
     B, L, V = 3, 19, 8192
     if kind == "no_old":
@@ -116,26 +80,19 @@ def test_options_fused(cuda, kind, mode):
     check(ref, got, kind)
 
 
-@pytest.mark.parametrize("mode", ["auto", "cluster"])
-def test_temperature_other_than_one(cuda, mode):
-    """The row-resident kernel does not do temperature != 1 (falls back to the sweeps); auto does."""
-    os.environ["MLLM_GRPO_FWD_BWD_MODE"] = mode
+def test_temperature_other_than_one(cuda):
     logits, inputs = make_case(2, 9, 4096, seed=63, old="noisy")
-    ref, got = run_fused(logits, inputs, cuda, expect_fused=(mode == "auto"), temperature=0.7)
+    ref, got = run_fused(logits, inputs, cuda, temperature=0.7)
     check(ref, got, "temperature")
 
 
-@pytest.mark.parametrize("mode", ["auto", "cluster"])
-def test_unaligned_vocab(cuda, mode):
-    os.environ["MLLM_GRPO_FWD_BWD_MODE"] = mode
+def test_unaligned_vocab(cuda):
     logits, inputs = make_case(2, 9, 4099, seed=64, old="noisy")
-    ref, got = run_fused(logits, inputs, cuda, expect_fused=(mode == "auto"))
+    ref, got = run_fused(logits, inputs, cuda)
     check(ref, got, "V=4099")
 
 
-@pytest.mark.parametrize("mode", ["auto", "cluster"])
-def test_fused_inplace_and_padded_stride(cuda, mode):
-    os.environ["MLLM_GRPO_FWD_BWD_MODE"] = mode
+def test_fused_inplace_and_padded_stride(cuda):
     logits, inputs = make_case(2, 12, 4096, seed=65, old="wide")
     ref, got = run_fused(logits, inputs, cuda, inplace=True)
     check(ref, got, "in place")
@@ -166,8 +123,8 @@ def test_fused_equals_two_sweeps_closely(cuda):
     args = (x, din["input_ids"], din["labels"], din["advantages"], din["total_valid_token_count"],
             din["old_per_token_logps"], din["ref_per_token_logps"])
     a = G.grpo_value_and_grad(*args, shifted=True, cfg=G.LossConfig(beta=0.04))
-    os.environ["MLLM_GRPO_FWD_BWD_MODE"] = "sweeps"
-    b = G.grpo_value_and_grad(*args, shifted=True, cfg=G.LossConfig(beta=0.04))
+    with plan_override(sweeps=True):
+        b = G.grpo_value_and_grad(*args, shifted=True, cfg=G.LossConfig(beta=0.04))
     torch.cuda.synchronize()
     assert (a["per_token_logps"] - b["per_token_logps"]).abs().max() < 2e-5
     assert abs(a["loss"].item() - b["loss"].item()) < 1e-6
@@ -175,17 +132,13 @@ def test_fused_equals_two_sweeps_closely(cuda):
     assert (da - db).abs().max() <= 0.01 * db.abs().max()
 
 
-@pytest.mark.parametrize("mode,cluster,threads", [("auto", 1, 512), ("auto", 1, 128), ("auto", 2, 256),
-                                                  ("auto", 4, 256), ("auto", 4, 128), ("auto", 8, 128),
-                                                  ("auto", 0, 0), ("cluster", 0, 0), ("sweeps", 0, 0)])
+@pytest.mark.parametrize("sweeps,cluster,threads,batch,staged", [
+    (0, 1, 512, 0, -1), (0, 1, 128, 0, 0), (0, 1, 64, 0, 0), (0, 1, 256, 0, 1), (0, 2, 256, 0, -1),
+    (0, 4, 256, 0, -1), (0, 4, 128, 6, -1), (0, 8, 128, 10, -1), (0, 2, 128, 8, -1), (0, 0, 0, 0, -1),
+    (1, 0, 0, 0, -1)])
 @pytest.mark.parametrize("kind", ["kl", "softcap", "shifted_tail"])
-def test_every_fwd_bwd_mode(cuda, mode, cluster, threads, kind):
-    """All implementations behind mllm_grpo_fwd_bwd give the oracle's answer."""
-    os.environ["MLLM_GRPO_FWD_BWD_MODE"] = mode
-    if cluster:
-        os.environ["MLLM_GRPO_L2_CLUSTER"] = str(cluster)
-    if threads:
-        os.environ["MLLM_GRPO_L2_THREADS"] = str(threads)
+def test_every_fwd_bwd_plan(cuda, sweeps, cluster, threads, batch, staged, kind):
+    """Every plan behind mllm_grpo_fwd_bwd gives the oracle's answer."""
     kw, attrs = dict(old="wide", ref=True), dict(beta=0.04)
     V = 16384
     if kind == "softcap":
@@ -193,5 +146,6 @@ def test_every_fwd_bwd_mode(cuda, mode, cluster, threads, kind):
     elif kind == "shifted_tail":
         V = 8 * 1013  # slices of unequal length
     logits, inputs = make_case(3, 23, V, seed=70, **kw)
-    ref, got = run_fused(logits, inputs, cuda, expect_fused=(mode != "sweeps"), **attrs)
-    check(ref, got, f"{mode} cl={cluster} th={threads} {kind}")
+    with plan_override(sweeps=bool(sweeps), cluster=cluster, threads=threads, load_batch=batch, staged=staged):
+        ref, got = run_fused(logits, inputs, cuda, expect_fused=not sweeps, **attrs)
+    check(ref, got, f"sweeps={sweeps} cl={cluster} th={threads} batch={batch} staged={staged} {kind}")

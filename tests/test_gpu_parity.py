@@ -422,26 +422,35 @@ def test_eager_gradient_in_forward(cuda, scale):
 
 
 def test_minus_infinity_logits(cuda):
-    """Vocabulary entries masked with -inf: log-probs, loss and dlogits stay exact; only the entropy
-    monitor of such a row is not finite (0 * -inf in its sum), which is the documented limitation."""
+    """Vocabulary entries masked with -inf: log-probs, loss and dlogits stay exact, and the entropy
+    monitor counts such entries as 0 like the reference's p * log(p + 1e-9) does
+    (MLLM_JAX/train_modules/__init__.py:138)."""
+    from mllm_jax_b200._lib import plan_override
+
     B, L, V = 2, 6, 4096
     logits, inputs = make_case(B, L, V, seed=48, old="none")
     logits[:, :, 1000:1500] = float("-inf")
+    logits[0, 1, 3000:] = float("-inf")  # one row has more of them, the others keep the common path
     inputs["input_ids"] = inputs["input_ids"] % 1000  # chosen tokens are finite
     ref = O.reference_value_and_grad(logits, inputs)
+    assert torch.isfinite(ref["token_entropy"]).all()
     x = logits.to(cuda)
     din = to_device(inputs, cuda)
-    for mode in ("auto", "sweeps"):
-        os.environ["MLLM_GRPO_FWD_BWD_MODE"] = mode
-        try:
+    for kw in (dict(), dict(sweeps=True), dict(cluster=2, threads=128), dict(cluster=1, threads=256, staged=1)):
+        with plan_override(**kw):
             out = G.grpo_value_and_grad(x, din["input_ids"], din["labels"], din["advantages"],
                                         din["total_valid_token_count"], None, None, shifted=True)
-        finally:
-            os.environ.pop("MLLM_GRPO_FWD_BWD_MODE", None)
         assert (out["per_token_logps"].cpu() - ref["per_token_logps"]).abs().max() <= LP_ATOL
+        assert (out["token_entropy"].cpu() - ref["token_entropy"]).abs().max() <= ENT_ATOL, kw
         assert_loss_close(out["loss"].item(), ref["loss"].item())
-        assert_dlogits_close(out["dlogits"], ref["dlogits"], what=f"-inf logits {mode}")
+        assert_dlogits_close(out["dlogits"], ref["dlogits"], what=f"-inf logits {kw}")
         assert (out["dlogits"][:, :, 1000:1500] == 0).all()
+    # temperature != 1: the entropy's own pair of sums is repaired the same way
+    ref_t = O.reference_value_and_grad(logits, inputs, temperature=0.7)
+    out = G.grpo_value_and_grad(x, din["input_ids"], din["labels"], din["advantages"],
+                                din["total_valid_token_count"], None, None, shifted=True,
+                                cfg=G.LossConfig(temperature=0.7))
+    assert (out["token_entropy"].cpu() - ref_t["token_entropy"]).abs().max() <= ENT_ATOL
 
 
 def test_extreme_logits_and_tiny_vocab(cuda):
@@ -589,8 +598,41 @@ def test_ppo_actor_critic_terms(cuda):
     assert x.grad is not None and x.grad.abs().max() > 0
     assert sorted(out) == sorted(["loss", "policy_loss", "value_loss", "entropy", "value_pred_mean", "return_mean",
                                   "per_token_logps"])
-    with pytest.raises(NotImplementedError):
-        G.ppo_actor_critic_terms(x, vg, to_device(inputs, cuda), entropy_coef=0.01)
+
+
+@pytest.mark.parametrize("temperature", [1.0, 0.7])
+@pytest.mark.parametrize("softcap", [None, 30.0])
+def test_ppo_entropy_coef_reaches_the_logits(cuda, temperature, softcap):
+    """loss = policy_loss + value_coef * value_loss - entropy_coef * entropy (plugins/training/ppo/module.py:140):
+    with entropy_coef != 0 the entropy's gradient is added to dlogits inside the backward sweep."""
+    logits, inputs = make_case(3, 21, 1544, seed=64, old="wide", per_token_adv=True, sigma=3.0 if softcap else 2.0)
+    logits[0, 2, 100:300] = float("-inf")
+    g = torch.Generator().manual_seed(65)
+    values = torch.randn(3, 21, generator=g)
+    inputs = {**inputs, "returns": torch.randn(3, 20, generator=g)}
+    coef = 0.37
+    xr = logits.float().requires_grad_(True)
+    capped = xr if softcap is None else torch.tanh(xr / softcap) * softcap
+    ref_p = O.ppo_policy_call(capped, inputs, temperature=temperature, detach_entropy=False)
+    ref_v = O.ppo_value_call(values, inputs, value_clip_range=0.2)
+    ref_loss = ref_p["policy_loss"] + 0.5 * ref_v["value_loss"] - coef * ref_p["entropy"]
+    ref_loss.backward()
+    x = logits.to(cuda).requires_grad_(True)
+    if softcap is None:
+        out = G.ppo_actor_critic_terms(x, values.to(cuda), to_device(inputs, cuda), temperature=temperature,
+                                       entropy_coef=coef)
+        loss = out["loss"]
+    else:  # the PPO module has no soft-cap; drive the operator directly
+        din = to_device(inputs, cuda)
+        o = G.grpo_token_loss(x, din["input_ids"], din["labels"], din["advantages"], din["total_valid_token_count"],
+                              din["old_per_token_logps"], temperature=temperature, epsilon_low=0.2, epsilon_high=0.2,
+                              softcap=softcap, entropy_grad=True)
+        m = din["labels"][:, 1:].float()
+        loss = o["loss"] + 0.5 * ref_v["value_loss"].item() - coef * (o["token_entropy"] * m).sum() / (m.sum() + 1e-8)
+    loss.backward()
+    torch.cuda.synchronize()
+    assert_loss_close(loss.item(), ref_loss.item())
+    assert_dlogits_close(x.grad, xr.grad, what=f"entropy_coef temperature={temperature} softcap={softcap}")
 
 
 @pytest.mark.parametrize("V", [18992, 50000, 151936])

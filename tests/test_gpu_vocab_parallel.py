@@ -1,9 +1,10 @@
 """Vocabulary-parallel paths on real GPUs.
 
 World size 1 always runs (the fused sharded kernel then exchanges with itself, which exercises the
-publish / wait / merge protocol and both epoch parities on one GPU).  With two or more GPUs a
-two-rank job is spawned: every rank checks the NCCL path and the fused peer-store path against the
-CPU oracle, including several back-to-back calls without any barrier in between."""
+publish / wait / merge protocol and both epoch parities on one GPU).  With more GPUs, jobs of 2, 4
+and 8 ranks are spawned (as many as the box has): every rank checks the NCCL path and the fused
+peer-store path against the CPU oracle, including several back-to-back calls without any barrier in
+between, and a token-parallel job checks the row-sharded mode the reference's own runs use."""
 import os
 import socket
 
@@ -79,38 +80,118 @@ def test_fused_sharded_kernel_world_size_one(cuda):
     _spawn(1)
 
 
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ranks_nccl_and_fused(cuda, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _spawn(world)
+
+
+def _run_token_parallel_rank(rank, world, port, ret):
+    import mllm_jax_b200 as G
+    from mllm_jax_b200.vocab_parallel import TokenParallelLoss
+    from oracle import grpo_oracle as O
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        per, L, V = 3, 33, 5000
+        B = per * world
+        logits, inputs = make_case(B, L, V, seed=93, old="wide", ref=True)
+        attrs = dict(beta=0.04, epsilon_low=0.2, epsilon_high=0.3)
+        ref = O.reference_value_and_grad(logits, inputs, **attrs)  # the whole batch, global normaliser
+        sl = slice(rank * per, (rank + 1) * per)
+        din = to_device({k: (v[sl] if isinstance(v, torch.Tensor) else v) for k, v in inputs.items()}, dev)
+        tp = TokenParallelLoss(G.LossConfig(**attrs))
+        out = tp.value_and_grad(logits[sl].to(dev), din["input_ids"], din["labels"], din["advantages"],
+                                din["total_valid_token_count"], din["old_per_token_logps"],
+                                din["ref_per_token_logps"], shifted=True)
+        torch.cuda.synchronize()
+        assert_loss_close(out["loss"].item(), ref["loss"].item(), what="sum of the ranks' losses")
+        assert (out["per_token_logps"].cpu() - ref["per_token_logps"][sl]).abs().max() <= LP_ATOL
+        assert_dlogits_close(out["dlogits"], ref["dlogits"][sl], what=f"token-parallel rank {rank}")
+        ret[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
 @pytest.mark.timeout(300)
-def test_two_ranks_nccl_and_fused(cuda):
+def test_token_parallel_two_ranks(cuda):
+    """Rows split over ranks (the reference's dp/fsdp batch sharding, plugins/training/runner/grpo_gsm8k.py:282)
+    with the global total_valid_token_count (:770): the ranks' losses add up to the oracle's loss of the whole
+    batch and every rank's dlogits are its rows of the oracle's gradient."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    _spawn(2)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_run_token_parallel_rank, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert dict(ret) == {0: "ok", 1: "ok"}
 
 
 @pytest.mark.timeout(120)
-def test_missing_peer_times_out_with_status(cuda):
+@pytest.mark.parametrize("rows", [3, 6000])
+def test_missing_peer_times_out_with_status(cuda, rows):
     """Failure detection without a GPU fault: rank 0 of a pretended 2-rank job runs alone, so the
-    words of rank 1 never arrive.  Every wait gives up after its wall-clock limit, the kernel ends
-    normally, the context stays usable and MLLM_GRPO_DEV_WAIT_TIMEOUT is raised for the host."""
+    words of rank 1 never arrive.  The first waits give up after their wall-clock limit and every
+    later row sees the raised bit and does not wait, so the whole call costs about one limit however
+    many rows it has; the kernel ends normally, the loss is NaN, no gradient is written for the rows
+    that gave up, MLLM_GRPO_DEV_WAIT_TIMEOUT is raised for the host and the context stays usable."""
+    import time
+
     import mllm_jax_b200 as G
     from mllm_jax_b200 import _lib
 
-    B, L, V = 1, 4, 512
+    B, L, V = 1, rows + 1, 512
     logits, inputs = make_case(B, L, V, seed=92, old="none", mask_kind="ones")
     din = to_device(inputs, cuda)
     x = logits[:, :-1].contiguous().to(cuda)
-    p = G.TokenLossProblem(x, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"], 3.0, None, None,
-                           G.LossConfig(), scored_rows=L - 1, vocab=V, vocab_start=0, vocab_total=2 * V)
+    p = G.TokenLossProblem(x, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"], float(rows), None,
+                           None, G.LossConfig(), scored_rows=L - 1, vocab=V, vocab_start=0, vocab_total=2 * V)
     nbytes = int(_lib.load().mllm_grpo_exchange_bytes(p.N, 2))
     mine = torch.zeros(nbytes, dtype=torch.uint8, device=cuda)
     absent_peer = torch.zeros(nbytes, dtype=torch.uint8, device=cuda)  # stands in for rank 1's buffer
     p.peer_ptrs, p.shard_rank, p.n_shards, p.exchange_epoch = [mine.data_ptr(), absent_peer.data_ptr()], 0, 2, 1
+    p.peer_wait_ms = 500
     p.alloc_dlogits()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
     p.run("mllm_grpo_fwd_bwd_sharded")
     torch.cuda.synchronize()
+    took = time.perf_counter() - t0
+    assert 0.4 <= took <= 5.0, took  # one limit (plus scheduling), not one per row or per wave
     assert G.ops.check_device_status(p) & _lib.DEV_WAIT_TIMEOUT
+    assert torch.isnan(p.loss).all() and torch.isnan(p.per_token_logps).all()
+    assert (p.dlogits == 0).all()
+    # the bit is sticky: a call that starts with it set does not wait at all
+    p.exchange_epoch = 2
+    t0 = time.perf_counter()
+    p.run("mllm_grpo_fwd_bwd_sharded")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.4 and torch.isnan(p.loss).all()
     # the context is still healthy: an ordinary call works afterwards
-    q = G.TokenLossProblem(x, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"], 3.0, None, None,
-                           G.LossConfig(), scored_rows=L - 1)
+    q = G.TokenLossProblem(x, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"], float(rows), None,
+                           None, G.LossConfig(), scored_rows=L - 1)
     q.run("mllm_grpo_fwd")
     torch.cuda.synchronize()
     assert torch.isfinite(q.loss).all() and G.ops.check_device_status(q) == 0
+
+
+def test_sharded_entry_needs_a_status_word(cuda):
+    import mllm_jax_b200 as G
+    from mllm_jax_b200 import _lib
+
+    logits, inputs = make_case(1, 4, 512, seed=94, old="none", mask_kind="ones")
+    din = to_device(inputs, cuda)
+    x = logits[:, :-1].contiguous().to(cuda)
+    p = G.TokenLossProblem(x, din["input_ids"][:, 1:], din["labels"][:, 1:], din["advantages"], 3.0, None, None,
+                           G.LossConfig(), scored_rows=3, vocab=512, vocab_start=0, vocab_total=512)
+    buf = torch.zeros(int(_lib.load().mllm_grpo_exchange_bytes(p.N, 1)), dtype=torch.uint8, device=cuda)
+    p.peer_ptrs, p.shard_rank, p.n_shards, p.exchange_epoch = [buf.data_ptr()], 0, 1, 1
+    p.alloc_dlogits()
+    p.device_status = None
+    with pytest.raises(_lib.GrpoError) as e:
+        p.run("mllm_grpo_fwd_bwd_sharded")
+    assert e.value.status == 1
