@@ -273,6 +273,41 @@ typedef struct mllm_ppo_value_args {
 int mllm_ppo_value_loss(const mllm_ppo_value_args* args, void* stream);
 int64_t mllm_ppo_value_workspace_bytes(int64_t n_seqs, int64_t seq_rows);
 
+/* lm_head projection folded into the forward of the loss: logits = hidden x weight^T
+ * (logits = self.lm_head(hidden_states), MLLM_JAX/language/qwen2/modular_qwen2.py:182, feeding
+ * MLLM_JAX/train_modules/__init__.py:124-138) are produced tile by tile on the tensor cores
+ * (tcgen05.mma into tensor memory, operands staged by TMA) and reduced there to the per-row
+ * (max, sumexp, sum e*y, chosen-or-0) of mllm_grpo_fwd_partials; the [n_rows, vocab] logits never reach
+ * HBM.  The vocabulary is cut into mllm_lm_head_splits() column ranges whose partials land in
+ * partials[split, row, 4]; mllm_grpo_combine with gathered_partials = partials and
+ * n_shards = mllm_lm_head_splits() then finishes the forward exactly as for vocabulary shards
+ * (per_token_logps, token_entropy, lse, grad_coef, loss).  The logits are the f32 accumulators themselves
+ * (no rounding to bf16 in between), soft-capped when softcap > 0.
+ *   hidden [n_rows, hidden_dim] bf16, rows hidden_stride elements apart;
+ *   weight [vocab, hidden_dim] bf16 (one row per vocabulary entry), rows weight_stride elements apart;
+ *   hidden_dim a multiple of 64, strides multiples of 8 elements, bases 16-byte aligned, else
+ *   MLLM_GRPO_ERR_UNSUPPORTED / _ALIGNMENT.  Entropy only at temperature 1 (the combine step's rule).
+ * Asynchronous on the stream, allocates nothing.  A pipeline wait that runs out (never in normal
+ * operation) raises MLLM_GRPO_DEV_WAIT_TIMEOUT in *device_status and the call's partials are void. */
+typedef struct mllm_lm_head_args {
+  uint64_t struct_size; /* sizeof(mllm_lm_head_args) */
+  int64_t n_rows;       /* B*T scored rows */
+  int64_t vocab;
+  int64_t hidden_dim;
+  int64_t hidden_stride;
+  int64_t weight_stride;
+  float softcap;        /* 0 = off */
+  int32_t flags;        /* MLLM_GRPO_FLAG_SKIP_ENTROPY */
+  const void* hidden;
+  const void* weight;
+  const int32_t* chosen_ids; /* [n_rows] */
+  void* partials;            /* mllm_lm_head_partials_bytes(n_rows, vocab) bytes, 16-byte aligned */
+  int32_t* device_status;    /* optional */
+} mllm_lm_head_args;
+int mllm_lm_head_partials(const mllm_lm_head_args* args, void* stream);
+int32_t mllm_lm_head_splits(int64_t n_rows, int64_t vocab);
+int64_t mllm_lm_head_partials_bytes(int64_t n_rows, int64_t vocab);
+
 /* Bytes of loss_terms scratch a problem of n_tokens = B*T needs. */
 int64_t mllm_grpo_workspace_bytes(int64_t n_tokens);
 

@@ -21,6 +21,7 @@ EXPORTS = (
     "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count", "mllm_grpo_fwd_static_scratch",
     "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_exchange_bytes", "mllm_grpo_set_plan_override",
     "mllm_grpo_entropy_stats", "mllm_grpo_scale_grad", "mllm_ppo_value_loss", "mllm_ppo_value_workspace_bytes",
+    "mllm_lm_head_partials", "mllm_lm_head_splits", "mllm_lm_head_partials_bytes",
 )
 
 
@@ -62,6 +63,19 @@ class PpoValueArgs(C.Structure):
     ]
 
 
+class LmHeadArgs(C.Structure):
+    """Mirror of `struct mllm_lm_head_args`."""
+
+    _fields_ = [
+        ("struct_size", C.c_uint64),
+        ("n_rows", C.c_int64), ("vocab", C.c_int64), ("hidden_dim", C.c_int64), ("hidden_stride", C.c_int64),
+        ("weight_stride", C.c_int64),
+        ("softcap", C.c_float), ("flags", C.c_int32),
+        ("hidden", C.c_void_p), ("weight", C.c_void_p), ("chosen_ids", C.c_void_p), ("partials", C.c_void_p),
+        ("device_status", C.c_void_p),
+    ]
+
+
 class GrpoError(RuntimeError):
     def __init__(self, fn: str, status: int, text: str, cuda: str = ""):
         self.status = status
@@ -91,6 +105,12 @@ def load():
         fn.restype = C.c_int
     lib.mllm_ppo_value_loss.argtypes = [C.POINTER(PpoValueArgs), C.c_void_p]
     lib.mllm_ppo_value_loss.restype = C.c_int
+    lib.mllm_lm_head_partials.argtypes = [C.POINTER(LmHeadArgs), C.c_void_p]
+    lib.mllm_lm_head_partials.restype = C.c_int
+    lib.mllm_lm_head_splits.argtypes = [C.c_int64, C.c_int64]
+    lib.mllm_lm_head_splits.restype = C.c_int32
+    lib.mllm_lm_head_partials_bytes.argtypes = [C.c_int64, C.c_int64]
+    lib.mllm_lm_head_partials_bytes.restype = C.c_int64
     lib.mllm_ppo_value_workspace_bytes.argtypes = [C.c_int64, C.c_int64]
     lib.mllm_ppo_value_workspace_bytes.restype = C.c_int64
     lib.mllm_grpo_workspace_bytes.argtypes = [C.c_int64]

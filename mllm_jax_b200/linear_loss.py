@@ -11,8 +11,10 @@ The GEMMs are library calls (cuBLAS through torch: bf16 operands, f32 accumulati
 gradient summed over chunks in f32); the loss and its gradient are this package's kernels.  On one
 B200 at 32768 x 3584 -> 151936 with 8192-row chunks a step takes 81.6 ms with the weight gradient
 (three GEMMs at 1.31 PFLOP/s, the loss kernels hidden behind them) and 55 ms without.
-A single kernel that keeps the logits tile in tensor memory and never writes it at all is the next
-step beyond this file.
+`lm_head_forward` goes one step further for the forward: the logits tile lives in tensor memory only
+(hand-written tcgen05 / TMA kernel, mllm_lm_head_partials) and is reduced there to the per-row softmax
+statistics, so forward-only passes (reference-model log-probs, the first PPO epoch's old log-probs, the
+loss value itself) never write or read a logits tensor at all.
 """
 from __future__ import annotations
 
@@ -20,7 +22,74 @@ from typing import Optional
 
 import torch
 
+from . import _lib
 from .ops import LossConfig, TokenLossProblem
+
+
+def lm_head_forward(hidden: torch.Tensor, weight: torch.Tensor, token_ids: torch.Tensor,
+                    mask: Optional[torch.Tensor] = None, advantages: Optional[torch.Tensor] = None,
+                    total_valid_token_count=None, old_per_token_logps: Optional[torch.Tensor] = None,
+                    ref_per_token_logps: Optional[torch.Tensor] = None, *, cfg: Optional[LossConfig] = None,
+                    workspace: Optional[torch.Tensor] = None) -> dict:
+    """Forward of lm_head + loss without logits in HBM.
+
+    hidden [B, T, H] (or [N, H]) bf16, weight [V, H] bf16 (logits = hidden @ weight.T, never stored),
+    token_ids [B, T] aligned with the rows.  With `advantages` given the whole forward runs (loss, residuals
+    lse / grad_coef for a later backward); without, only per_token_logps, token_entropy and lse are meaningful
+    (the reference-model pass, train_modules/__init__.py:129-132, and plugins/training/update/ppo.py:39-43).
+    Two launches: the tensor-core kernel writes per-row partials for each vocabulary range, and
+    mllm_grpo_combine merges them and runs the per-token epilogue.  H must be a multiple of 64.
+    The logits are the f32 accumulators (not rounded to bf16 on the way)."""
+    cfg = cfg or LossConfig()
+    if hidden.dim() == 2:
+        hidden = hidden.unsqueeze(0)
+        token_ids = token_ids.reshape(1, -1)
+    if not hidden.is_cuda:
+        raise RuntimeError("lm_head_forward needs CUDA tensors: the kernels have no CPU path")
+    if hidden.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise TypeError("hidden and weight must be bfloat16")
+    B, T, H = hidden.shape
+    V = weight.shape[0]
+    if weight.shape[1] != H or hidden.stride(2) != 1 or weight.stride(1) != 1 or hidden.stride(0) != T * hidden.stride(1):
+        raise ValueError(f"hidden {tuple(hidden.shape)} / weight {tuple(weight.shape)}: need [B, T, H] rows evenly "
+                         "spaced and [V, H], both with unit stride along H")
+    if cfg.temperature != 1.0 and cfg.compute_entropy:
+        raise ValueError("the entropy of the folded forward needs temperature 1 (pass compute_entropy=False)")
+    dev = hidden.device
+    N = B * T
+    lib = _lib.load()
+    splits = int(lib.mllm_lm_head_splits(N, V))
+    nbytes = int(lib.mllm_lm_head_partials_bytes(N, V))
+    if workspace is None:
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    elif workspace.numel() * workspace.element_size() < nbytes or workspace.data_ptr() % 16:
+        raise ValueError(f"workspace must hold {nbytes} bytes at a 16-byte aligned address")
+    forward_only = advantages is None
+    if forward_only:
+        advantages = torch.zeros(B, dtype=torch.float32, device=dev)
+    # side arrays, outputs and residuals exactly as for materialised logits; no logits tensor is bound
+    prob = TokenLossProblem.__new__(TokenLossProblem)
+    TokenLossProblem._init_side(prob, B, T, T, V, dev, token_ids, mask, advantages, total_valid_token_count,
+                                old_per_token_logps, ref_per_token_logps, cfg)
+    a = _lib.LmHeadArgs()
+    a.n_rows, a.vocab, a.hidden_dim = N, V, H
+    a.hidden_stride, a.weight_stride = hidden.stride(1), weight.stride(0)
+    a.softcap = float(cfg.softcap) if cfg.softcap else 0.0
+    a.flags = 0 if cfg.compute_entropy else _lib.FLAG_SKIP_ENTROPY
+    a.hidden, a.weight = hidden.data_ptr(), weight.data_ptr()
+    a.chosen_ids, a.partials = prob.chosen_ids.data_ptr(), workspace.data_ptr()
+    a.device_status = prob.device_status.data_ptr()
+    with torch.cuda.device(dev):
+        _lib.call("mllm_lm_head_partials", a, torch.cuda.current_stream().cuda_stream)
+        g = prob.args()
+        g.gathered_partials, g.n_shards = workspace.data_ptr(), splits
+        _lib.call("mllm_grpo_combine", g, torch.cuda.current_stream().cuda_stream)
+    prob._keepalive = (hidden, weight, workspace)
+    out = {"per_token_logps": prob.per_token_logps, "token_entropy": prob.token_entropy, "lse": prob.lse.view(B, T),
+           "problem": prob, "splits": splits}
+    if not forward_only:
+        out["loss"] = prob.loss.reshape(())
+    return out
 
 
 def linear_grpo_value_and_grad(hidden: torch.Tensor, weight: torch.Tensor, token_ids: torch.Tensor,

@@ -63,15 +63,25 @@ class TokenLossProblem:
         B, L, Vfull = logits.shape
         if logits.stride(2) != 1 or (B > 1 and logits.stride(0) != L * logits.stride(1)):
             raise ValueError("logits must have unit stride on the vocabulary and rows evenly spaced")
-        self.cfg = cfg
         self.logits = logits
-        self.B, self.L, self.T = B, L, int(scored_rows)
-        self.V = int(vocab) if vocab is not None else Vfull
         self.row_stride = logits.stride(1)
+        self._init_side(B, L, int(scored_rows), int(vocab) if vocab is not None else Vfull, logits.device, chosen_ids,
+                        mask, advantages, total_valid_token_count, old_logps, ref_logps, cfg, vocab_start=vocab_start,
+                        vocab_total=vocab_total)
+
+    def _init_side(self, B, L, T, V, dev, chosen_ids, mask, advantages, total_valid_token_count, old_logps, ref_logps,
+                   cfg: LossConfig, vocab_start: int = 0, vocab_total: Optional[int] = None):
+        """Everything but the logits: geometry, per-token side arrays, outputs and residuals.  Also used on its
+        own by callers that have no logits tensor (the folded lm_head forward)."""
+        if not hasattr(self, "logits"):
+            self.logits = None
+            self.row_stride = V
+        self.cfg = cfg
+        self.B, self.L, self.T = B, L, T
+        self.V = V
         self.vocab_start = int(vocab_start)
         self.vocab_total = int(vocab_total) if vocab_total is not None else self.vocab_start + self.V
         N = B * self.T
-        dev = logits.device
         self.N = N
 
         def side(t, name, dtype):
@@ -186,7 +196,7 @@ class TokenLossProblem:
             a.exchange_epoch = self.exchange_epoch
         else:
             a = self._args = self.args()
-        with torch.cuda.device(self.logits.device):
+        with torch.cuda.device(self.device_status.device):
             _lib.call(entry, a, _stream())
 
 

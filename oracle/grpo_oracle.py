@@ -218,6 +218,13 @@ def sft_call(logits: torch.Tensor, inputs: Mapping[str, Any], *, label_ignore_id
     return {"loss": loss, "token_count": valid.to(torch.int32).sum()}         # :41-45
 
 
+def lm_head_logits(hidden: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """logits = self.lm_head(hidden_states) (MLLM_JAX/language/qwen2/modular_qwen2.py:182; a bias-free Dense) in
+    float64 from the exact bf16 operands: hidden [..., H] x weight [V, H]^T.  The checker of the folded
+    lm_head + loss kernels, whose logits are f32 accumulators that are never rounded to bf16."""
+    return hidden.double() @ weight.double().t()
+
+
 def analytic_rows(x: np.ndarray, chosen: np.ndarray, mask: np.ndarray, adv: np.ndarray,
                   old: Optional[np.ndarray], ref: Optional[np.ndarray], total_valid: float, *, beta: float = 0.0,
                   temperature: float = 1.0, epsilon_low: float = 0.2, epsilon_high: float = 0.3,

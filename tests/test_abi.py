@@ -17,7 +17,7 @@ HEADER = os.path.join(ROOT, "include", "mllm_grpo.h")
 def _declared_functions():
     text = open(HEADER).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(mllm_(?:grpo|ppo)_[a-z_0-9]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(mllm_(?:grpo|ppo|lm_head)_[a-z_0-9]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol(built_lib):
@@ -63,6 +63,35 @@ def test_value_struct_matches_c_layout(tmp_path):
     assert int(out[0]) == C.sizeof(_lib.PpoValueArgs)
     for f, off in zip(fields, out[1:]):
         assert getattr(_lib.PpoValueArgs, f).offset == int(off), f
+
+
+def test_lm_head_struct_matches_c_layout_and_validation(tmp_path, built_lib):
+    fields = [f[0] for f in _lib.LmHeadArgs._fields_]
+    src = tmp_path / "layout.c"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "mllm_grpo.h"', "int main(void){",
+             'printf("%zu\\n", sizeof(mllm_lm_head_args));']
+    lines += [f'printf("%zu\\n", offsetof(mllm_lm_head_args, {f}));' for f in fields]
+    lines += ["return 0;}"]
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", f"-I{os.path.join(ROOT, 'include')}", str(src), "-o",
+                    str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert int(out[0]) == C.sizeof(_lib.LmHeadArgs)
+    for f, off in zip(fields, out[1:]):
+        assert getattr(_lib.LmHeadArgs, f).offset == int(off), f
+    lib = _lib.load()
+    a = _lib.LmHeadArgs()
+    assert lib.mllm_lm_head_partials(C.byref(a), None) == 4  # struct size
+    a.struct_size = C.sizeof(_lib.LmHeadArgs)
+    assert lib.mllm_lm_head_partials(C.byref(a), None) == 2  # shape
+    a.n_rows, a.vocab, a.hidden_dim, a.hidden_stride, a.weight_stride = 256, 1000, 128, 128, 128
+    assert lib.mllm_lm_head_partials(C.byref(a), None) == 1  # null pointers
+    a.hidden = a.weight = a.chosen_ids = a.partials = 0x1000
+    a.hidden_dim = a.hidden_stride = a.weight_stride = 72
+    assert lib.mllm_lm_head_partials(C.byref(a), None) == 7  # hidden size must be a multiple of 64
+    assert lib.mllm_lm_head_splits(256, 151936) == 38 and lib.mllm_lm_head_splits(0, 5) == 0
+    assert lib.mllm_lm_head_partials_bytes(256, 151936) == 38 * 256 * 16
 
 
 def test_value_loss_validation(built_lib):

@@ -1,0 +1,89 @@
+"""lm_head projection folded into the forward of the loss (tcgen05 / TMA kernel).
+
+The oracle computes logits = hidden x weight^T in float64 from the same bf16 operands
+(MLLM_JAX/language/qwen2/modular_qwen2.py:182) and runs the loss restatement on them; the kernel's
+logits are f32 tensor-core accumulators that never leave the chip, so log-probs are held to the usual
+2e-3 abs, entropy to 5e-4 and the loss to 1e-4 rel."""
+import pytest
+import torch
+
+import mllm_jax_b200 as G
+from mllm_jax_b200.linear_loss import lm_head_forward
+from oracle import grpo_oracle as O
+from tests.util import ENT_ATOL, LP_ATOL, assert_loss_close, make_case
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(B, T, H, V, seed, scale=0.5, **kw):
+    g = torch.Generator().manual_seed(seed)
+    hidden = torch.randn(B, T, H, generator=g).to(torch.bfloat16)
+    weight = (torch.randn(V, H, generator=g) * scale / H ** 0.5 * 4).to(torch.bfloat16)
+    logits64 = O.lm_head_logits(hidden, weight)                      # [B, T, V] float64
+    _, inputs = make_case(B, T + 1, V, seed=seed + 1, old="none", **kw)
+    ids, mask = inputs["input_ids"][:, 1:], inputs["labels"][:, 1:]
+    lp0 = torch.log_softmax(logits64, -1).gather(-1, ids.long()[..., None])[..., 0].float()
+    old = lp0 + 0.3 * torch.randn(B, T, generator=g)
+    ref_lp = lp0 + 0.1 * torch.randn(B, T, generator=g)
+    nv = float(mask.sum()) or 1.0
+    z = torch.zeros(B, 1, dtype=ids.dtype)
+    oin = {"input_ids": torch.cat([z, ids], 1), "labels": torch.cat([z, mask], 1), "advantages": inputs["advantages"],
+           "total_valid_token_count": nv, "old_per_token_logps": old, "ref_per_token_logps": ref_lp}
+    shifted = torch.cat([logits64, logits64[:, :1]], 1)              # the unscored last position
+    return hidden, weight, ids, mask, inputs["advantages"], nv, old, ref_lp, oin, shifted
+
+
+@pytest.mark.parametrize("B,T,H,V", [
+    (1, 128, 64, 256),       # exactly one tile, one k-block
+    (2, 150, 192, 1000),     # ragged rows (300 = 2 tiles + 44) and a ragged last vocabulary tile
+    (1, 130, 128, 10240),    # 40 vocabulary tiles: three splits, accumulator ping-pong inside a CTA
+    (3, 50, 896, 4099),      # vocabulary not a multiple of 8, Qwen2.5-0.5B's hidden size
+])
+def test_folded_forward_matches_oracle(cuda, B, T, H, V):
+    hidden, weight, ids, mask, adv, nv, old, ref_lp, oin, shifted = _case(B, T, H, V, seed=300 + H)
+    ref = O.reference_call(shifted, oin, beta=0.04, dtype=torch.float64)
+    out = lm_head_forward(hidden.to(cuda), weight.to(cuda), ids.to(cuda), mask.to(cuda), adv.to(cuda), nv,
+                          old.to(cuda), ref_lp.to(cuda), cfg=G.LossConfig(beta=0.04))
+    torch.cuda.synchronize()
+    assert G.ops.check_device_status(out["problem"]) == 0
+    assert (out["per_token_logps"].cpu().double() - ref["per_token_logps"]).abs().max() <= LP_ATOL
+    assert (out["token_entropy"].cpu().double() - ref["token_entropy"]).abs().max() <= ENT_ATOL
+    assert_loss_close(out["loss"].item(), ref["loss"].item())
+    # the residuals feed the ordinary backward: lse against the oracle's logsumexp
+    lse = torch.logsumexp(shifted[:, :-1], -1)
+    assert (out["lse"].cpu().double() - lse).abs().max() <= LP_ATOL
+
+
+def test_folded_forward_softcap_and_tile_edges(cuda):
+    """Soft-capped logits, and chosen tokens on the first / last column of vocabulary tiles and splits."""
+    B, T, H, V = 1, 64, 128, 256 * 17 + 8
+    hidden, weight, ids, mask, adv, nv, old, ref_lp, oin, shifted = _case(B, T, H, V, seed=77, scale=6.0)
+    edges = torch.tensor([0, 255, 256, 511, 256 * 9 - 1, 256 * 9, V - 1, V - 8])
+    ids[0, :edges.numel()] = edges.to(ids.dtype)
+    oin["input_ids"][0, 1:1 + edges.numel()] = edges.to(ids.dtype)
+    ref = O.reference_call(shifted, oin, softcap=30.0, dtype=torch.float64)
+    out = lm_head_forward(hidden.to(cuda), weight.to(cuda), ids.to(cuda), mask.to(cuda), adv.to(cuda), nv,
+                          old.to(cuda), None, cfg=G.LossConfig(softcap=30.0))
+    torch.cuda.synchronize()
+    assert G.ops.check_device_status(out["problem"]) == 0
+    assert (out["per_token_logps"].cpu().double() - ref["per_token_logps"]).abs().max() <= LP_ATOL
+    assert (out["token_entropy"].cpu().double() - ref["token_entropy"]).abs().max() <= ENT_ATOL
+    assert_loss_close(out["loss"].item(), ref["loss"].item())
+
+
+def test_folded_forward_only_logprobs(cuda):
+    """No advantages: the reference-model pass (log-probs and entropy only)."""
+    hidden, weight, ids, *_rest, oin, shifted = _case(2, 70, 256, 3000, seed=78)
+    lp = torch.log_softmax(shifted[:, :-1], -1).gather(-1, ids.long()[..., None])[..., 0]
+    out = lm_head_forward(hidden.to(cuda), weight.to(cuda), ids.to(cuda))
+    torch.cuda.synchronize()
+    assert (out["per_token_logps"].cpu().double() - lp).abs().max() <= LP_ATOL
+
+
+def test_folded_forward_rejects_what_it_cannot_run(cuda):
+    hidden = torch.zeros(1, 4, 72, dtype=torch.bfloat16, device=cuda)  # hidden size not a multiple of 64
+    weight = torch.zeros(16, 72, dtype=torch.bfloat16, device=cuda)
+    ids = torch.zeros(1, 4, dtype=torch.int32, device=cuda)
+    with pytest.raises(G.GrpoError) as e:
+        lm_head_forward(hidden, weight, ids)
+    assert e.value.status == 7
