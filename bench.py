@@ -65,6 +65,7 @@ def parse():
     ap.add_argument("--rows", type=int, default=0, help="override the number of sequences (tuning only)")
     ap.add_argument("--vp-mode", default="fused", choices=["fused", "nccl"],
                     help="vocab-parallel: exchange inside the kernel over peer stores, or three kernels + NCCL all-gather")
+    ap.add_argument("--hidden", type=int, default=3584, help="--fold-lm-head: hidden size (a multiple of 64)")
     ap.add_argument("--fold-lm-head", action="store_true",
                     help="time the lm_head projection folded into the loss (hidden x weight -> log-probs without "
                          "logits in HBM) instead of the loss on materialised logits; 1 GPU")
@@ -519,9 +520,9 @@ def main():
     if args.impl == "reference":
         return run_reference(args)
     if args.fold_lm_head:
-        from mllm_jax_b200 import lm_head_bench
-
-        return lm_head_bench.main(args)
+        line = run_fold_lm_head(Job(args), args, args.steps, args.warmup)
+        print(json.dumps(line))
+        return
 
     from mllm_jax_b200 import _lib, synth
 
@@ -549,6 +550,17 @@ def main():
                      launches_per_step=rf["step"]["launches_per_step"], chunks=r["config"]["chunks"])
         extra.append(e)
 
+    fold = None
+    if job.world == 1 and args.workload == "cfg1" and args.extra is None:
+        # the row next to the path: lm_head folded into the forward (tensor-core kernel), measured briefly
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            f = run_fold_lm_head(job, args, steps=3, warmup=3)
+            fold = {k: f[k] for k in ("metric", "value", "ms_per_step", "config", "roofline", "library_path", "parity",
+                                      "device_status")}
+        except torch.OutOfMemoryError as exc:
+            fold = {"skipped": f"out of device memory ({str(exc)[:60]})"}
     cpu = None
     if job.rank == 0 and job.world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(args, synth.parse_workload(args.workload))
@@ -563,8 +575,109 @@ def main():
             "config": res["config"], "loss": res["loss"], "device_status": res["device_status"],
             "valid_tokens_per_s": res["valid_tokens_per_s"], "roofline": res["roofline"], "exchange": res["exchange"],
             "parity": res["parity"], "cpu_baseline": cpu, "e2e": res["e2e"], "gpu_launches": res["gpu_launches"],
-            "clocks": res["clocks"], "extra": extra,
+            "clocks": res["clocks"], "extra": extra, "fold_lm_head": fold,
         }))
+
+
+def run_fold_lm_head(job, args, steps, warmup):
+    """lm_head folded into the forward of the loss (1 GPU): hidden [N, H] x weight [V, H]^T -> per-token log-probs,
+    entropy and loss with the logits held in tensor memory only, timed beside the library GEMM + loss kernel that
+    materialises them.  Shapes: the workload's rows and vocabulary, H = 3584 (Qwen2.5-7B) unless --hidden."""
+    import mllm_jax_b200 as G
+    from mllm_jax_b200 import _lib, synth
+    from mllm_jax_b200.linear_loss import lm_head_forward
+    from oracle import grpo_oracle as O
+
+    if job.world != 1:
+        raise SystemExit("--fold-lm-head is a 1-GPU measurement")
+    dev = job.dev
+    w = synth.parse_workload(args.workload)
+    if args.rows:
+        w = synth.scaled(w, n_seqs=args.rows)
+    if args.vocab:
+        w = synth.scaled(w, vocab=args.vocab)
+    B, T, V, H = w.n_seqs, w.seq_len, w.vocab, args.hidden
+    N = B * T
+    g = torch.Generator(device=dev).manual_seed(1234 + args.seed)
+    hidden = torch.randn(B, T, H, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    weight = (torch.randn(V, H, generator=g, device=dev, dtype=torch.float32) * (w.sigma / H ** 0.5)).to(torch.bfloat16)
+    side = synth.make_inputs(w, seed=args.seed, device=str(dev), want_logits=False)
+    cfg = G.LossConfig(epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high, beta=w.beta, softcap=w.softcap)
+    # old / ref log-probs around the true ones of THIS projection: one folded forward-only pass supplies them
+    lp = lm_head_forward(hidden, weight, side["token_ids"], cfg=cfg)["per_token_logps"].clone()
+    old = lp + (side["old_logps"] - side["exact_logps"])
+    ref = lp + (side["ref_logps"] - side["exact_logps"])
+    work = torch.empty(int(_lib.load().mllm_lm_head_partials_bytes(N, V)), dtype=torch.uint8, device=dev)
+    call = (hidden, weight, side["token_ids"], side["mask"], side["advantages"], side["total_valid"], old, ref)
+
+    def fused():
+        return lm_head_forward(*call, cfg=cfg, workspace=work)
+
+    logits = torch.empty(B, T, V, dtype=torch.bfloat16, device=dev)
+    wt = weight.t()
+
+    def library():
+        torch.matmul(hidden, wt, out=logits)
+        return G.grpo_token_loss_flat(logits, side["token_ids"], side["mask"], side["advantages"], side["total_valid"],
+                                      old, ref, epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high, beta=w.beta,
+                                      softcap=w.softcap)
+
+    def timed(fn, steps, warmup):
+        for _ in range(max(warmup, 3)):
+            out = fn()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            out = fn()
+        ev1.record()
+        torch.cuda.synchronize()
+        return ev0.elapsed_time(ev1) / steps, out
+
+    sampler = ClockSampler(job.local)
+    sampler.start()
+    time.sleep(0.15)
+    launches0 = _lib.launch_count()
+    ms_fused, out = timed(fused, steps, warmup)
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop()
+    ms_lib, out_lib = timed(library, max(3, steps // 2), 3)
+    flops = 2.0 * N * V * H
+    peak = float(job.peaks.get("bf16_tflops_sustained", 1400.0))
+    tf = flops / (ms_fused * 1e-3) / 1e12
+    # parity on sampled rows against float64 logits of the same operands
+    rows = sample_rows(N, 48).to(dev)
+    x64 = O.lm_head_logits(hidden.view(N, H)[rows].cpu(), weight.cpu()).numpy()
+    pick = lambda t: t.reshape(N)[rows].double().cpu().numpy()  # noqa: E731
+    import numpy as np
+    advN = side["advantages"][:, None].expand(-1, T).reshape(N)
+    an = O.analytic_rows(x64, side["token_ids"].reshape(N)[rows].long().cpu().numpy(), pick(side["mask"]), pick(advN),
+                         pick(old), pick(ref), side["total_valid"], beta=w.beta, epsilon_low=w.epsilon_low,
+                         epsilon_high=w.epsilon_high, softcap=w.softcap, want_grad=False)
+    lp_abs = float(np.abs(pick(out["per_token_logps"]) - an["lp"]).max())
+    ent_abs = float(np.abs(pick(out["token_entropy"]) - an["entropy_guard"]).max())
+    terms_abs = float(np.abs(pick(out["problem"].loss_terms) - an["loss_terms"]).max())
+    return ({
+        "metric": "lm_head + GRPO loss forward tokens/s (logits never in HBM)", "value": N / (ms_fused * 1e-3),
+        "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms_fused,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 operands / f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": w.name + "-fold-lm-head", "rows": N, "vocab": V, "hidden": H,
+                   "l2": "weight (%.2f GB) and hidden (%.2f GB) exceed the 126 MB L2" % (V * H * 2 / 1e9, N * H * 2 / 1e9)},
+        "loss": float(out["loss"].item()), "device_status": int(out["problem"].device_status.item()),
+        "roofline": {"bound": "tensor", "kernel": "lm_head_stats_kernel (tcgen05.mma 128x256x16 bf16, TMEM accumulators)",
+                     "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "peak_kind": job.peak_kind +
+                     " (library bf16 GEMM sustained)", "flops_per_launch": flops, "ms_per_launch": ms_fused,
+                     "traffic": None,
+                     "note": "ms_per_launch covers the tensor-core kernel plus the two small merge kernels"},
+        "library_path": {"what": "torch.matmul (library GEMM) writing bf16 logits + mllm_grpo_fwd reading them",
+                         "ms_per_step": ms_lib, "tflops": flops / (ms_lib * 1e-3) / 1e12,
+                         "logits_bytes": 2.0 * N * V, "loss": float(out_lib["loss"].item())},
+        "parity": {"rows": int(rows.numel()), "lp_abs": lp_abs, "entropy_abs": ent_abs, "loss_terms_abs": terms_abs,
+                   "ok": bool(lp_abs <= 2e-3 and ent_abs <= 5e-4),
+                   "against": "closed-form f64 CPU oracle on float64 logits of the same bf16 operands"},
+        "gpu_launches": launches, "clocks": clocks,
+    })
 
 
 def run_reference(args):
