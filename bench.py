@@ -65,6 +65,11 @@ def parse():
     ap.add_argument("--rows", type=int, default=0, help="override the number of sequences (tuning only)")
     ap.add_argument("--vp-mode", default="fused", choices=["fused", "nccl"],
                     help="vocab-parallel: exchange inside the kernel over peer stores, or three kernels + NCCL all-gather")
+    ap.add_argument("--plan", default=None,
+                    help="tuning only: sweeps,cluster,threads,load_batch,staged for mllm_grpo_set_plan_override "
+                         "(0 / -1 = automatic), e.g. 0,2,128,6,-1")
+    ap.add_argument("--self-exchange", action="store_true",
+                    help="tuning only, 1 GPU: run the vocabulary-sharded kernel as a single shard that exchanges with itself")
     ap.add_argument("--hidden", type=int, default=3584, help="--fold-lm-head: hidden size (a multiple of 64)")
     ap.add_argument("--fold-lm-head", action="store_true",
                     help="time the lm_head projection folded into the loss (hidden x weight -> log-probs without "
@@ -184,20 +189,28 @@ class Job:
         torch.cuda.set_device(self.local)
         self.dev = torch.device("cuda", self.local)
         self.dist = None
+        self.self_exchange = bool(getattr(args, "self_exchange", False)) and self.world == 1
         if self.world > 1:
             import torch.distributed as dist
 
             dist.init_process_group("nccl", device_id=self.dev)
             self.dist = dist
+        elif self.self_exchange:
+            import torch.distributed as dist
+
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29533")
+            dist.init_process_group("gloo", rank=0, world_size=1)
+            self.dist = dist
         self.peaks, self.peak_kind = peaks()
 
     def barrier(self):
-        if self.dist is not None:
+        if self.dist is not None and self.world > 1:
             self.dist.barrier()
         torch.cuda.synchronize()
 
     def max_over_ranks(self, x: float) -> float:
-        if self.dist is None:
+        if self.dist is None or self.world == 1:
             return x
         t = torch.tensor([x], device=self.dev, dtype=torch.float64)
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
@@ -235,7 +248,7 @@ def parity_check(job: Job, w, data, out, mode: str, v_local: int) -> dict:
     rows = sample_rows(n_local, count).to(dev)
     x = data["logits"].view(n_local, -1)[rows]
     d = out["dlogits"].view(n_local, -1)[rows]
-    if mode == "vocab":
+    if mode == "vocab" and job.world > 1:
         xs = torch.empty(job.world, *x.shape, dtype=x.dtype, device=dev)
         ds = torch.empty(job.world, *d.shape, dtype=d.dtype, device=dev)
         dist.all_gather_into_tensor(xs.view(-1), x.contiguous().view(-1))
@@ -259,7 +272,7 @@ def parity_check(job: Job, w, data, out, mode: str, v_local: int) -> dict:
         d_rel = float((err[nz] / rowmax[nz]).max()) if nz.any() else 0.0
         zero_ok = bool((err[~nz] == 0).all())
         res = [lp_abs, ent_abs, d_rel, 0.0 if zero_ok else 1.0]
-    if mode == "token" and dist is not None:
+    if mode == "token" and dist is not None and job.world > 1:
         t = torch.tensor(res, device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         res = t.tolist()
@@ -285,7 +298,9 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
         w = synth.scaled(w, n_seqs=args.rows, name=w.name + f"-B{args.rows}")
     cfg = G.LossConfig(epsilon_low=w.epsilon_low, epsilon_high=w.epsilon_high, beta=w.beta, softcap=w.softcap)
     N, V = w.n_tokens, w.vocab
-    mode = "single" if world == 1 else args.parallelism
+    mode = "single" if world == 1 and not job.self_exchange else args.parallelism
+    if job.self_exchange:
+        mode = "vocab"
     if mode == "vocab" and V % world:
         return {"workload": w.name, "skipped": f"vocabulary {V} does not split over {world} ranks"}
     if mode == "token" and w.n_seqs % world:
@@ -346,7 +361,8 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
             except Exception as exc:  # symmetric memory unavailable on this box
                 vp_note = f"peer exchange buffers could not be set up ({type(exc).__name__}: {str(exc)[:80]})"
                 ok = torch.zeros(1, device=dev)
-            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if world > 1:
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
             if ok.item() == 0:
                 vp_mode = "nccl"
                 vp_note = vp_note or "another rank could not set up the peer exchange buffers"
@@ -394,7 +410,7 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     t_k = []
     for i in range(3 + min(steps, 10)):
-        if dist is not None and mode == "vocab":
+        if dist is not None and mode == "vocab" and world > 1:
             dist.barrier()  # ranks enter the exchanging kernel together, as in the timed loop's steady state
         evs[0].record()
         launch()
@@ -527,7 +543,9 @@ def main():
     from mllm_jax_b200 import _lib, synth
 
     job = Job(args)
-    _lib.load()
+    lib = _lib.load()
+    if args.plan:
+        lib.mllm_grpo_set_plan_override(*[int(v) for v in args.plan.split(",")])
     res = run_workload(job, args.workload, args.steps, args.warmup, main=True)
     if "skipped" in res:
         raise SystemExit(res["skipped"])
