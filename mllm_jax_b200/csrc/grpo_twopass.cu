@@ -193,7 +193,8 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
       parts[tid] = make_float4(got[0], got[1], got[2], got[3]);
     }
   }
-  __syncthreads();
+  // Unsharded: thread 0 reads slots it wrote itself (CL == 1) or acquired at the cluster barrier (CL > 1).
+  if (SHARDED) __syncthreads();  // parts[] were written by threads 0..k-1
   if (tid == 0) {
     const float4 m = SHARDED ? merge_partials(parts, p.n_shards) : merge_partials(slots, CL);
     RowStats all;
