@@ -87,3 +87,38 @@ def test_folded_forward_rejects_what_it_cannot_run(cuda):
     with pytest.raises(G.GrpoError) as e:
         lm_head_forward(hidden, weight, ids)
     assert e.value.status == 7
+
+
+@pytest.mark.timeout(600)
+def test_folded_forward_full_vocabulary_and_hidden_size(cuda):
+    """The benchmark's shape per row (H = 3584, V = 151936: 594 vocabulary tiles in 38 splits, 56 k-blocks) on
+    300 rows; 24 sampled rows against float64 logits of the same operands."""
+    import numpy as np
+
+    B, T, H, V = 1, 300, 3584, 151936
+    g = torch.Generator(device=cuda).manual_seed(5)
+    hidden = torch.randn(B, T, H, generator=g, device=cuda).to(torch.bfloat16)
+    weight = (torch.randn(V, H, generator=g, device=cuda) * (2.0 / H ** 0.5)).to(torch.bfloat16)
+    gc = torch.Generator().manual_seed(6)
+    ids = torch.randint(0, V, (B, T), generator=gc, dtype=torch.int64).to(torch.int32)
+    ids[0, :4] = torch.tensor([0, V - 1, 255, 256], dtype=torch.int32)
+    mask = (torch.rand(B, T, generator=gc) < 0.7).float()
+    adv = torch.randn(B, generator=gc)
+    nv = float(mask.sum())
+    lp_dev = lm_head_forward(hidden, weight, ids.to(cuda))["per_token_logps"].cpu()
+    old = lp_dev + 0.3 * torch.randn(B, T, generator=gc)
+    out = lm_head_forward(hidden, weight, ids.to(cuda), mask.to(cuda), adv.to(cuda), nv, old.to(cuda), None,
+                          cfg=G.LossConfig(epsilon_low=0.2, epsilon_high=0.2))
+    torch.cuda.synchronize()
+    assert G.ops.check_device_status(out["problem"]) == 0
+    rows = torch.cat([torch.arange(4), torch.randint(4, T, (20,), generator=gc)]).unique()
+    x64 = O.lm_head_logits(hidden[0, rows.to(cuda)].cpu(), weight.cpu()).numpy()
+    pick = lambda t: t.reshape(-1)[rows].double().cpu().numpy()  # noqa: E731
+    an = O.analytic_rows(x64, ids.reshape(-1)[rows].long().numpy(), pick(mask), np.full(rows.numel(), adv.item()),
+                         pick(old), None, nv, epsilon_low=0.2, epsilon_high=0.2, want_grad=False)
+    assert np.abs(pick(out["per_token_logps"]) - an["lp"]).max() <= LP_ATOL
+    assert np.abs(pick(out["token_entropy"]) - an["entropy_guard"]).max() <= ENT_ATOL
+    assert np.abs(pick(out["lse"]) - an["lse"]).max() <= LP_ATOL
+    assert np.allclose(pick(out["problem"].loss_terms), an["loss_terms"], atol=2e-3)
+    # the loss is the fixed-order sum of the per-token terms
+    assert_loss_close(out["loss"].item(), out["problem"].loss_terms.double().sum().item() / nv)
