@@ -283,6 +283,9 @@ int64_t mllm_ppo_value_workspace_bytes(int64_t n_seqs, int64_t seq_rows);
  * n_shards = mllm_lm_head_splits() then finishes the forward exactly as for vocabulary shards
  * (per_token_logps, token_entropy, lse, grad_coef, loss).  The logits are the f32 accumulators themselves
  * (no rounding to bf16 in between), soft-capped when softcap > 0.
+ * tp-sharded head (lm_head kernel partitioned over "tp", MLLM_JAX/utils.py:245): every rank calls it on its own
+ * weight rows [vocab_start, vocab_start + vocab) with GLOBAL chosen ids; the ranks' partials, all-gathered into
+ * [k * splits, n_rows, 4], go through one mllm_grpo_combine with n_shards = k * splits.
  *   hidden [n_rows, hidden_dim] bf16, rows hidden_stride elements apart;
  *   weight [vocab, hidden_dim] bf16 (one row per vocabulary entry), rows weight_stride elements apart;
  *   hidden_dim a multiple of 64, strides multiples of 8 elements, bases 16-byte aligned, else
@@ -296,6 +299,8 @@ typedef struct mllm_lm_head_args {
   int64_t hidden_dim;
   int64_t hidden_stride;
   int64_t weight_stride;
+  int64_t vocab_start;  /* global id of weight row 0 (0 unless this call holds one vocabulary shard of the head) */
+  int64_t vocab_total;  /* global vocabulary size; 0 means vocab_start + vocab */
   float softcap;        /* 0 = off */
   int32_t flags;        /* MLLM_GRPO_FLAG_SKIP_ENTROPY */
   const void* hidden;

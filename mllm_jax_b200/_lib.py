@@ -69,7 +69,7 @@ class LmHeadArgs(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint64),
         ("n_rows", C.c_int64), ("vocab", C.c_int64), ("hidden_dim", C.c_int64), ("hidden_stride", C.c_int64),
-        ("weight_stride", C.c_int64),
+        ("weight_stride", C.c_int64), ("vocab_start", C.c_int64), ("vocab_total", C.c_int64),
         ("softcap", C.c_float), ("flags", C.c_int32),
         ("hidden", C.c_void_p), ("weight", C.c_void_p), ("chosen_ids", C.c_void_p), ("partials", C.c_void_p),
         ("device_status", C.c_void_p),

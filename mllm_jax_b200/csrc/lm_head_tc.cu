@@ -41,7 +41,7 @@ constexpr unsigned long long kWaitNs = 2000000000ull;  // 2 s per wait
 constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 
 struct Params {
-  int64_t n_rows, vocab, hidden;
+  int64_t n_rows, vocab, hidden, vocab_start, vocab_total;
   int m_tiles, n_vtiles, splits, tiles_per_split, k_blocks;
   float softcap;
   int want_entropy;
@@ -237,11 +237,13 @@ lm_head_stats_kernel(const __grid_constant__ CUtensorMap map_hidden, const __gri
     const int row_in_tile = quarter * 32 + lane;
     const int64_t row = int64_t(m_tile) * kBM + row_in_tile;
     const bool row_ok = row < p.n_rows;
-    int64_t c = row_ok ? p.chosen_ids[row] : 0;
-    if (row_ok && (c < 0 || c >= p.vocab)) {
-      c = c < 0 ? 0 : p.vocab - 1;
+    int64_t c = row_ok ? p.chosen_ids[row] : 0;  // global id
+    if (row_ok && (c < 0 || c >= p.vocab_total)) {
+      c = c < 0 ? 0 : p.vocab_total - 1;
       if (p.device_status) atomicOr(p.device_status, MLLM_GRPO_DEV_ID_CLAMPED);
     }
+    c -= p.vocab_start;  // column among this call's weight rows
+    if (c < 0 || c >= p.vocab) c = -1;  // another vocabulary shard owns the chosen token
     const bool cap = p.softcap > 0.f;
     const SoftCap sc(cap ? p.softcap : 1.0f);
     float m = kNegInit, s = 0.f, u = 0.f, yc = 0.f;
@@ -384,6 +386,7 @@ int mllm_lm_head_partials(const mllm_lm_head_args* a, void* stream) {
   if (a->struct_size != sizeof(mllm_lm_head_args)) return MLLM_GRPO_ERR_STRUCT_SIZE;
   if (a->n_rows <= 0 || a->vocab <= 0 || a->hidden_dim <= 0) return MLLM_GRPO_ERR_BAD_SHAPE;
   if (a->hidden_stride < a->hidden_dim || a->weight_stride < a->hidden_dim) return MLLM_GRPO_ERR_BAD_SHAPE;
+  if (a->vocab_start < 0 || (a->vocab_total > 0 && a->vocab_start + a->vocab > a->vocab_total)) return MLLM_GRPO_ERR_BAD_SHAPE;
   if (!a->hidden || !a->weight || !a->chosen_ids || !a->partials) return MLLM_GRPO_ERR_NULL_POINTER;
   // TMA: 16-byte aligned bases and row pitches; whole 64-element k-blocks keep the pipeline uniform
   if ((a->hidden_dim % lmh::kBK) || (a->hidden_stride % 8) || (a->weight_stride % 8)) return MLLM_GRPO_ERR_UNSUPPORTED;
@@ -396,6 +399,8 @@ int mllm_lm_head_partials(const mllm_lm_head_args* a, void* stream) {
   lmh::Params p;
   p.n_rows = a->n_rows;
   p.vocab = a->vocab;
+  p.vocab_start = a->vocab_start;
+  p.vocab_total = a->vocab_total > 0 ? a->vocab_total : a->vocab_start + a->vocab;
   p.hidden = a->hidden_dim;
   p.m_tiles = int((a->n_rows + lmh::kBM - 1) / lmh::kBM);
   p.n_vtiles = int((a->vocab + lmh::kBN - 1) / lmh::kBN);

@@ -30,8 +30,14 @@ def lm_head_forward(hidden: torch.Tensor, weight: torch.Tensor, token_ids: torch
                     mask: Optional[torch.Tensor] = None, advantages: Optional[torch.Tensor] = None,
                     total_valid_token_count=None, old_per_token_logps: Optional[torch.Tensor] = None,
                     ref_per_token_logps: Optional[torch.Tensor] = None, *, cfg: Optional[LossConfig] = None,
-                    workspace: Optional[torch.Tensor] = None) -> dict:
+                    workspace: Optional[torch.Tensor] = None, vocab_start: int = 0,
+                    vocab_total: Optional[int] = None, group=None) -> dict:
     """Forward of lm_head + loss without logits in HBM.
+
+    tp-sharded head (lm_head kernel partitioned over "tp", MLLM_JAX/utils.py:245): pass this rank's weight rows
+    [vocab_start, vocab_start + V) with vocab_total and the process group; token_ids stay GLOBAL ids.  The ranks'
+    per-row partials (16 bytes per row and vocabulary range) are all-gathered and merged on every rank, so all
+    outputs are replicated.
 
     hidden [B, T, H] (or [N, H]) bf16, weight [V, H] bf16 (logits = hidden @ weight.T, never stored),
     token_ids [B, T] aligned with the rows.  With `advantages` given the whole forward runs (loss, residuals
@@ -69,11 +75,13 @@ def lm_head_forward(hidden: torch.Tensor, weight: torch.Tensor, token_ids: torch
         advantages = torch.zeros(B, dtype=torch.float32, device=dev)
     # side arrays, outputs and residuals exactly as for materialised logits; no logits tensor is bound
     prob = TokenLossProblem.__new__(TokenLossProblem)
-    TokenLossProblem._init_side(prob, B, T, T, V, dev, token_ids, mask, advantages, total_valid_token_count,
+    v_all = int(vocab_total) if vocab_total is not None else int(vocab_start) + V
+    TokenLossProblem._init_side(prob, B, T, T, v_all, dev, token_ids, mask, advantages, total_valid_token_count,
                                 old_per_token_logps, ref_per_token_logps, cfg)
     a = _lib.LmHeadArgs()
     a.n_rows, a.vocab, a.hidden_dim = N, V, H
     a.hidden_stride, a.weight_stride = hidden.stride(1), weight.stride(0)
+    a.vocab_start, a.vocab_total = int(vocab_start), int(vocab_total) if vocab_total is not None else int(vocab_start) + V
     a.softcap = float(cfg.softcap) if cfg.softcap else 0.0
     a.flags = 0 if cfg.compute_entropy else _lib.FLAG_SKIP_ENTROPY
     a.hidden, a.weight = hidden.data_ptr(), weight.data_ptr()
@@ -81,10 +89,19 @@ def lm_head_forward(hidden: torch.Tensor, weight: torch.Tensor, token_ids: torch
     a.device_status = prob.device_status.data_ptr()
     with torch.cuda.device(dev):
         _lib.call("mllm_lm_head_partials", a, torch.cuda.current_stream().cuda_stream)
+        parts, n_parts = workspace, splits
+        if group is not None:
+            import torch.distributed as dist
+
+            k = dist.get_world_size(group)
+            mine = workspace[:nbytes]
+            parts = torch.empty(k * nbytes, dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(parts, mine, group=group)  # [k, splits, N, 4] f32: rank-major vocabulary ranges
+            n_parts = k * splits
         g = prob.args()
-        g.gathered_partials, g.n_shards = workspace.data_ptr(), splits
+        g.gathered_partials, g.n_shards = parts.data_ptr(), n_parts
         _lib.call("mllm_grpo_combine", g, torch.cuda.current_stream().cuda_stream)
-    prob._keepalive = (hidden, weight, workspace)
+    prob._keepalive = (hidden, weight, workspace, parts)
     out = {"per_token_logps": prob.per_token_logps, "token_entropy": prob.token_entropy, "lse": prob.lse.view(B, T),
            "problem": prob, "splits": splits}
     if not forward_only:

@@ -196,7 +196,7 @@ class TokenLossProblem:
             a.exchange_epoch = self.exchange_epoch
         else:
             a = self._args = self.args()
-        with torch.cuda.device(self.device_status.device):
+        with torch.cuda.device(self.per_token_logps.device):
             _lib.call(entry, a, _stream())
 
 

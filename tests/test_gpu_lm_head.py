@@ -122,3 +122,40 @@ def test_folded_forward_full_vocabulary_and_hidden_size(cuda):
     assert np.allclose(pick(out["problem"].loss_terms), an["loss_terms"], atol=2e-3)
     # the loss is the fixed-order sum of the per-token terms
     assert_loss_close(out["loss"].item(), out["problem"].loss_terms.double().sum().item() / nv)
+
+
+def test_folded_forward_on_a_vocabulary_shard(cuda):
+    """One vocabulary shard of a tp-sharded head (global ids, vocab_start): the partials of two shards, merged
+    by one combine over both shards' vocabulary ranges, reproduce the unsharded result."""
+    from mllm_jax_b200 import _lib
+
+    B, T, H, V = 2, 90, 128, 2 * 1000
+    hidden, weight, ids, mask, adv, nv, old, ref_lp, oin, shifted = _case(B, T, H, V, seed=91)
+    ref = O.reference_call(shifted, oin, dtype=torch.float64)
+    full = lm_head_forward(hidden.to(cuda), weight.to(cuda), ids.to(cuda), mask.to(cuda), adv.to(cuda), nv,
+                           old.to(cuda), None)
+    lib = _lib.load()
+    N, half = B * T, V // 2
+    splits = int(lib.mllm_lm_head_splits(N, half))
+    nbytes = int(lib.mllm_lm_head_partials_bytes(N, half))
+    both = torch.empty(2 * nbytes, dtype=torch.uint8, device=cuda)
+    hid, wt, idd = hidden.to(cuda), weight.to(cuda), ids.to(cuda).contiguous()
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    for r in range(2):  # what rank r of a 2-rank job computes; the all-gather is the concatenation
+        a = _lib.LmHeadArgs()
+        a.n_rows, a.vocab, a.hidden_dim, a.hidden_stride, a.weight_stride = N, half, H, H, H
+        a.vocab_start, a.vocab_total = r * half, V
+        a.hidden, a.weight = hid.data_ptr(), wt[r * half:(r + 1) * half].data_ptr()
+        a.chosen_ids, a.partials = idd.data_ptr(), both[r * nbytes:].data_ptr()
+        a.device_status = status.data_ptr()
+        _lib.call("mllm_lm_head_partials", a, torch.cuda.current_stream().cuda_stream)
+    prob = full["problem"]
+    g = prob.args()
+    g.gathered_partials, g.n_shards = both.data_ptr(), 2 * splits
+    prob.per_token_logps.fill_(float("nan"))
+    _lib.call("mllm_grpo_combine", g, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert (prob.per_token_logps.cpu().double() - ref["per_token_logps"]).abs().max() <= LP_ATOL
+    assert (prob.token_entropy.cpu().double() - ref["token_entropy"]).abs().max() <= ENT_ATOL
+    assert_loss_close(prob.loss.item(), ref["loss"].item())

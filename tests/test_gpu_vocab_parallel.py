@@ -63,6 +63,22 @@ def _run_rank(rank, world, port, ret):
             assert (out["token_entropy"].cpu() - ref["token_entropy"]).abs().max() <= ENT_ATOL, name
             assert_loss_close(out["loss"].item(), ref["loss"].item(), what=name)
             assert_dlogits_close(out["dlogits"], want_d, what=name)
+        if world > 1:
+            # tp-sharded lm_head folded into the forward: every rank multiplies by its own weight rows, the
+            # per-row partials are all-gathered (16 bytes per row and vocabulary range) and merged on every rank
+            from mllm_jax_b200.linear_loss import lm_head_forward
+
+            g = torch.Generator().manual_seed(95)
+            H = 128
+            hidden = torch.randn(B, L - 1, H, generator=g).to(torch.bfloat16)
+            weight = (torch.randn(V, H, generator=g) * 0.3).to(torch.bfloat16)
+            x64 = O.lm_head_logits(hidden, weight)
+            ids = inputs["input_ids"][:, 1:]
+            want = torch.log_softmax(x64, -1).gather(-1, ids.long()[..., None])[..., 0]
+            out = lm_head_forward(hidden.to(dev), weight[vp.start:vp.stop].contiguous().to(dev), ids.to(dev),
+                                  vocab_start=vp.start, vocab_total=V, group=dist.group.WORLD)
+            torch.cuda.synchronize()
+            assert (out["per_token_logps"].cpu().double() - want).abs().max() <= LP_ATOL, "sharded lm_head forward"
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()
