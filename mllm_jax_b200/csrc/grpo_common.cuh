@@ -123,28 +123,27 @@ __device__ __forceinline__ uint32_t bf16x2_min(uint32_t a, uint32_t b) {
 
 // Soft-cap y = cap*tanh(x/cap) (deprecated/MLLM_JAX/language/gemma/transformer.py:337-339).
 // |x| <= cap (the common case: cap = 30 is 7.5 sigma of Gemma-like logits): an odd polynomial
-// y = x*P(x^2) of degree 11 evaluated on the FMA pipe, absolute error of tanh 3e-7 (1e-5 in y at
-// cap 30) -- one SFU op per element is then left for the softmax exponential.  Beyond the cap:
-// cap - 2cap/(1 + e^(2x/cap)), two SFU ops, exact at saturation.  (tanh.approx would be 5e-4
-// relative, too coarse for a 2e-3 log-prob bound.)
+// y = x*P(x^2) of degree 9 evaluated on the FMA pipe, absolute error of tanh 2.8e-6 (8.5e-5 in y at
+// cap 30, i.e. below 2e-4 in a log-prob against a 2e-3 gate) -- one SFU op per element is then left
+// for the softmax exponential.  Beyond the cap: cap - 2cap/(1 + e^(2x/cap)), two SFU ops, exact at
+// saturation.  (tanh.approx would be 5e-4 relative, too coarse for a 2e-3 log-prob bound; a degree-11
+// polynomial, 3e-7, costs one more packed FMA per pair and pass.)
 struct SoftCap {
   float cap, icap, c1;
-  float d0, d1, d2, d3, d4, d5;  // tanh(z)/z ~ sum_k t_k z^(2k) on [-1, 1]; d_k = t_k / cap^(2k)
+  float d0, d1, d2, d3, d4;  // tanh(z)/z ~ sum_k t_k z^(2k) on [-1, 1]; d_k = t_k / cap^(2k)
   __device__ __forceinline__ explicit SoftCap(float cap_) : cap(cap_), icap(1.0f / cap_), c1(2.0f * kLog2e / cap_) {
     const float i2 = icap * icap;
-    d0 = 0.9999968409538269f;
-    d1 = -0.3332400321960449f * i2;
-    d2 = 0.13253529369831085f * i2 * i2;
-    d3 = -0.05097292736172676f * i2 * i2 * i2;
-    d4 = 0.016114233061671257f * i2 * i2 * i2 * i2;
-    d5 = -0.0028394809924066067f * i2 * i2 * i2 * i2 * i2;
+    d0 = 0.9999684691429138f;
+    d1 = -0.3326584994792938f * i2;
+    d2 = 0.12922197580337524f * i2 * i2;
+    d3 = -0.04330199584364891f * i2 * i2 * i2;
+    d4 = 0.008366995491087437f * i2 * i2 * i2 * i2;
   }
   __device__ __forceinline__ float y_far(float x) const { return fmaf(-2.0f * cap, rcpf(1.0f + ex2f(x * c1)), cap); }
   __device__ __forceinline__ float y(float x) const {
     if (fabsf(x) > cap) return y_far(x);
     const float q = x * x;
-    float p = fmaf(d5, q, d4);
-    p = fmaf(p, q, d3);
+    float p = fmaf(d4, q, d3);
     p = fmaf(p, q, d2);
     p = fmaf(p, q, d1);
     p = fmaf(p, q, d0);
@@ -153,8 +152,7 @@ struct SoftCap {
   // Both lanes of a pair at once; only valid when |x| <= cap in both lanes.
   __device__ __forceinline__ f32x2 y2_near(f32x2 x) const {
     const f32x2 q = mul2(x, x);
-    f32x2 p = fma2(pack2(d5, d5), q, pack2(d4, d4));
-    p = fma2(p, q, pack2(d3, d3));
+    f32x2 p = fma2(pack2(d4, d4), q, pack2(d3, d3));
     p = fma2(p, q, pack2(d2, d2));
     p = fma2(p, q, pack2(d1, d1));
     p = fma2(p, q, pack2(d0, d0));

@@ -79,3 +79,48 @@ def test_ppo_update_collects_old_logps_in_first_epoch():
     assert torch.equal(out["old_per_token_logps"], expect)
     assert entropy.item() == 3.0 and last["entropy"].item() == 11.0
     assert "old_per_token_logps" not in data  # the caller's dict is not modified
+
+
+def test_synthetic_shards_are_slices_of_one_tensor():
+    """Vocabulary and row shards of a workload are slices of the tensor the unsharded call builds, and old / ref
+    log-probs are the same in every mode (so runs at different GPU counts see the same problem)."""
+    import torch
+
+    from mllm_jax_b200 import synth
+
+    w = synth.scaled(synth.CONFIGS["cfg0"], n_seqs=6, seq_len=700, vocab=512, group=3)  # blocks straddle sequences
+    full = synth.make_inputs(w, seed=2)
+    for r in range(4):
+        sh = synth.make_inputs(w, seed=2, vocab_shard=(r, 4))
+        assert torch.equal(sh["logits"], full["logits"][:, :, r * 128:(r + 1) * 128])
+        assert torch.equal(sh["old_logps"], full["old_logps"]) and torch.equal(sh["ref_logps"], full["ref_logps"])
+    for r in range(3):
+        rs = synth.make_inputs(w, seed=2, row_shard=(r, 3))
+        assert torch.equal(rs["logits"], full["logits"][2 * r:2 * r + 2])
+        assert torch.equal(rs["old_logps"], full["old_logps"][2 * r:2 * r + 2])
+        assert torch.equal(rs["advantages"], full["advantages"][2 * r:2 * r + 2])
+        assert rs["total_valid"] == full["total_valid"]  # the normaliser stays global
+    assert not torch.equal(synth.make_inputs(w, seed=3)["logits"], full["logits"])
+    none = synth.make_inputs(w, seed=2, want_logits=False)
+    assert none["logits"] is None and torch.equal(none["exact_logps"], full["exact_logps"])
+
+
+def test_workload_names_and_chunking():
+    import pytest
+
+    import bench
+    from mllm_jax_b200 import synth
+
+    assert synth.parse_workload("cfg2").vocab == 128256
+    w = synth.parse_workload("cfg4-1048576")
+    assert w.n_tokens == 1048576 and w.vocab == 151936 and w.half_valid_runs
+    with pytest.raises(ValueError):
+        synth.parse_workload("cfg9")
+    # one GPU: 1M rows x 151936 = 318.6 GB -> 8 launches of 131072 rows over one 39.8 GB buffer
+    seqs, chunks = bench.chunking(w, w.n_seqs, w.vocab)
+    assert chunks == 8 and seqs * w.seq_len == 131072
+    # 8 GPUs vocabulary-sharded: 39.8 GB per GPU fits in one launch
+    assert bench.chunking(w, w.n_seqs, w.vocab // 8) == (w.n_seqs, 1)
+    # cfg1 never chunks
+    c1 = synth.CONFIGS["cfg1"]
+    assert bench.chunking(c1, c1.n_seqs, c1.vocab) == (c1.n_seqs, 1)
