@@ -122,26 +122,28 @@ __device__ __forceinline__ uint32_t bf16x2_min(uint32_t a, uint32_t b) {
 }
 
 // Soft-cap y = cap*tanh(x/cap) (deprecated/MLLM_JAX/language/gemma/transformer.py:337-339).
-// |x| <= cap (the common case: cap = 30 is 7.5 sigma of Gemma-like logits): an odd polynomial
-// y = x*P(x^2) of degree 9 evaluated on the FMA pipe, absolute error of tanh 2.8e-6 (8.5e-5 in y at
-// cap 30, i.e. below 2e-4 in a log-prob against a 2e-3 gate) -- one SFU op per element is then left
-// for the softmax exponential.  Beyond the cap: cap - 2cap/(1 + e^(2x/cap)), two SFU ops, exact at
-// saturation.  (tanh.approx would be 5e-4 relative, too coarse for a 2e-3 log-prob bound; a degree-11
-// polynomial, 3e-7, costs one more packed FMA per pair and pass.)
+// |x| <= 0.75 cap (the common case: 0.75 * 30 is 5.6 sigma of Gemma-like logits): an odd polynomial
+// y = x*P(x^2) of degree 9 evaluated on the FMA pipe, absolute error of tanh 2.6e-7 (8e-6 in y at
+// cap 30) -- one SFU op per element is then left for the softmax exponential.  Beyond that:
+// cap - 2cap/(1 + e^(2x/cap)), two SFU ops, exact at saturation.  (tanh.approx would be 5e-4
+// relative, too coarse for a 2e-3 log-prob bound.  Fitted over the whole |x| <= cap a degree-9
+// polynomial is 10x less accurate and broke the 1e-4 loss gate; degree 11 costs one more packed FMA
+// per pair and pass.)
 struct SoftCap {
-  float cap, icap, c1;
-  float d0, d1, d2, d3, d4;  // tanh(z)/z ~ sum_k t_k z^(2k) on [-1, 1]; d_k = t_k / cap^(2k)
-  __device__ __forceinline__ explicit SoftCap(float cap_) : cap(cap_), icap(1.0f / cap_), c1(2.0f * kLog2e / cap_) {
+  float cap, icap, c1, near;
+  float d0, d1, d2, d3, d4;  // tanh(z)/z ~ sum_k t_k z^(2k) on [-0.75, 0.75]; d_k = t_k / cap^(2k)
+  __device__ __forceinline__ explicit SoftCap(float cap_)
+      : cap(cap_), icap(1.0f / cap_), c1(2.0f * kLog2e / cap_), near(0.75f * cap_) {
     const float i2 = icap * icap;
-    d0 = 0.9999684691429138f;
-    d1 = -0.3326584994792938f * i2;
-    d2 = 0.12922197580337524f * i2 * i2;
-    d3 = -0.04330199584364891f * i2 * i2 * i2;
-    d4 = 0.008366995491087437f * i2 * i2 * i2 * i2;
+    d0 = 0.9999972581863403f;
+    d1 = -0.33323079347610474f * i2;
+    d2 = 0.13226120173931122f * i2 * i2;
+    d3 = -0.04928125441074371f * i2 * i2 * i2;
+    d4 = 0.012319567613303661f * i2 * i2 * i2 * i2;
   }
   __device__ __forceinline__ float y_far(float x) const { return fmaf(-2.0f * cap, rcpf(1.0f + ex2f(x * c1)), cap); }
   __device__ __forceinline__ float y(float x) const {
-    if (fabsf(x) > cap) return y_far(x);
+    if (fabsf(x) > near) return y_far(x);
     const float q = x * x;
     float p = fmaf(d4, q, d3);
     p = fmaf(p, q, d2);
@@ -149,7 +151,7 @@ struct SoftCap {
     p = fmaf(p, q, d0);
     return x * p;
   }
-  // Both lanes of a pair at once; only valid when |x| <= cap in both lanes.
+  // Both lanes of a pair at once; only valid when |x| <= near in both lanes.
   __device__ __forceinline__ f32x2 y2_near(f32x2 x) const {
     const f32x2 q = mul2(x, x);
     f32x2 p = fma2(pack2(d4, d4), q, pack2(d3, d3));

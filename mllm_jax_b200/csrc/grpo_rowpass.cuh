@@ -114,7 +114,7 @@ __device__ __forceinline__ void fold_vectors(RowAcc<ENT>& acc, const uint4 (&v)[
   const float mk = acc.m * kLog2e;
   const float mk2 = mk * inv_temp;
   if (CAP && ENT != 2) {
-    // Whole batch inside the cap (the common case): packed-pair polynomial tanh, two lanes per issue.
+    // Whole batch inside the polynomial's range (the common case): packed-pair polynomial tanh, two lanes per issue.
     uint32_t mn2 = v[0].x;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -124,7 +124,7 @@ __device__ __forceinline__ void fold_vectors(RowAcc<ENT>& acc, const uint4 (&v)[
       mn2 = bf16x2_min(mn2, v[i].w);
     }
     const float lo = fminf(bf16lo(mn2), bf16hi(mn2)), hi = fmaxf(bf16lo(mx2), bf16hi(mx2));
-    if (lo >= -sc.cap && hi <= sc.cap) {
+    if (lo >= -sc.near && hi <= sc.near) {
       const f32x2 kk = pack2(kLog2e, kLog2e), nmk = pack2(-mk, -mk);
       f32x2 s2 = pack2(0.f, 0.f), u2 = pack2(0.f, 0.f);
 #pragma unroll
@@ -370,7 +370,7 @@ __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, in
     if (CAP && !ENTG && idx != cv) {
       const uint32_t mx2 = bf16x2_max(bf16x2_max(w[0], w[1]), bf16x2_max(w[2], w[3]));
       const uint32_t mn2 = bf16x2_min(bf16x2_min(w[0], w[1]), bf16x2_min(w[2], w[3]));
-      near = fminf(bf16lo(mn2), bf16hi(mn2)) >= -sc.cap && fmaxf(bf16lo(mx2), bf16hi(mx2)) <= sc.cap;
+      near = fminf(bf16lo(mn2), bf16hi(mn2)) >= -sc.near && fmaxf(bf16lo(mx2), bf16hi(mx2)) <= sc.near;
     }
     if (!CAP && !ENTG && idx != cv) {
 #pragma unroll
@@ -380,7 +380,7 @@ __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, in
         o[j] = pack_bf16x2(a, c) ^ sgn;
       }
     } else if (CAP && near) {
-      // all eight inside the cap, chosen column elsewhere: packed-pair polynomial tanh
+      // all eight inside the polynomial's range, chosen column elsewhere: packed-pair polynomial tanh
       const f32x2 kk = pack2(kLog2e, kLog2e), oo = pack2(off, off);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
