@@ -133,6 +133,8 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
     if (p.ref_logps) prefetch_l2(p.ref_logps + n);
   }
 
+  constexpr bool kPrefetch = SHARDED && !SMEM;  // cluster slices: the held batch costs 24 registers and two CTAs per SM
+  const float row_mask = (kPrefetch && p.prefetch2 && p.mask) ? p.mask[n] : 1.0f;  // one broadcast load per warp
   const uint16_t* xs = x16;
   if (SMEM) {
     __syncthreads();  // the barrier is initialised
@@ -141,6 +143,13 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
   }
   const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, SMEM ? 3 : 2>(xs, ncol, p.inv_temperature, sc, red, keep);
   if (CAP && tid < 8 && cl_local >= 0 && cl_local < ncol) yc_own = sc.y(yc_own);
+  // Request the second pass's first batch now (rows that will get a gradient only): it arrives from L2 while
+  // the partials are merged, exchanged and the epilogue runs.
+  FirstBatch<UNROLL> first;
+  first.have = false;
+  if constexpr (kPrefetch) {
+    if (p.prefetch2) load_first_batch<THREADS, UNROLL, 2>(first, x16, d16, ncol, drop, row_mask != 0.f);
+  }
 
   if (CL > 1) {
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
@@ -222,7 +231,12 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
     bc[1] = o.lse;
   }
   __syncthreads();
-  row_pass2<THREADS, UNROLL, CAP, 2, SMEM ? 3 : -1>(xs, d16, ncol, bc[0], bc[1], cl_local, sc, drop);
+  if constexpr (kPrefetch) {
+    row_pass2<THREADS, UNROLL, CAP, 2, -1>(xs, d16, ncol, bc[0], bc[1], cl_local, sc, drop,
+                                           EntropyGrad{0.f, 0.f, 0.f, 1.f}, &first);
+  } else {
+    row_pass2<THREADS, UNROLL, CAP, 2, SMEM ? 3 : -1>(xs, d16, ncol, bc[0], bc[1], cl_local, sc, drop);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -357,7 +371,7 @@ void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, i
   bool sm = cl == 1 && aligned16 && ent != 2 && slice_bytes <= 48 * 1024 && slice_bytes >= 4096;
   if (f_sm >= 0) sm = f_sm != 0 && cl == 1 && aligned16 && ent != 2 && slice_bytes <= 99 * 1024;
   if (sm && f_th <= 0) th = 256;
-  if (f_un > 0) un = f_un;
+  if (f_un > 0) un = f_un % 100;
   *cluster = cl;
   *threads = th;
   *smem = sm;
@@ -373,6 +387,10 @@ cudaError_t launch_two_pass(const KernelParams& p, int ent, bool sharded, cudaSt
   bool smem = false;
   int unroll = 8;
   two_pass_plan(p, ent, sharded, &cluster, &threads, &smem, &unroll);
+  KernelParams q = p;
+  q.prefetch2 = g_force_batch.load(std::memory_order_relaxed) >= 100 ? 1 : 0;
+  return sharded ? launch_c<true>(q, ent, cluster, threads, unroll, smem, s)
+                 : launch_c<false>(q, ent, cluster, threads, unroll, smem, s);
   return sharded ? launch_c<true>(p, ent, cluster, threads, unroll, smem, s)
                  : launch_c<false>(p, ent, cluster, threads, unroll, smem, s);
 }
