@@ -217,6 +217,38 @@ class Job:
         return float(t.item())
 
 
+def config_dict(w, world: int, mode: str, parallelism: str, seed: int) -> dict:
+    """The `config` object of a line: the same for this package's arm and for the reference arm, which derives it
+    from the workload alone (the mask comes from the seeded side arrays, no logits needed)."""
+    from mllm_jax_b200 import synth
+
+    v_local = w.vocab // world if mode == "vocab" else w.vocab
+    seqs_local = w.n_seqs // world if mode == "token" else w.n_seqs
+    chunk_seqs, n_chunks = chunking(w, seqs_local, v_local)
+    rows_chunk = chunk_seqs * w.seq_len
+    wc = w
+    if n_chunks > 1:
+        total = chunk_seqs * (world if mode == "token" else 1)
+        wc = synth.scaled(w, n_seqs=total, group=min(w.group, total))
+    mask = synth.side_arrays(wc, seed)[2]
+    return {"workload": w.name, "rows": w.n_tokens, "vocab": w.vocab, "global_batch": w.n_seqs, "seq_len": w.seq_len,
+            "parallelism": parallelism,
+            "l2": "inputs (%.1f GB per GPU per launch) exceed the 126 MB L2" % (2.0 * v_local * rows_chunk / 1e9),
+            "chunks": None if n_chunks == 1 else
+            f"{n_chunks} launches per step over ONE buffer of {rows_chunk} rows ({2.0 * v_local * rows_chunk / 1e9:.1f} GB "
+            f"of logits per GPU): the full batch does not fit beside its gradient",
+            "mask_valid_fraction": float(mask.double().mean().item()),
+            "epsilon": [w.epsilon_low, w.epsilon_high], "beta": w.beta, "softcap": w.softcap}
+
+
+def default_parallelism(world: int, mode: str, seqs_local: int) -> str:
+    if world == 1:
+        return "single"
+    if mode == "token":
+        return f"token-parallel dp{world}: {seqs_local} sequences per rank, scalar loss all-reduce (NCCL)"
+    return f"vocab-parallel tp{world}, exchange: peer stores inside the kernel"
+
+
 def chunking(w, rows_local_seqs: int, v_local: int):
     """(sequences per chunk, chunks): the largest divisor of this rank's sequences whose logits fit CHUNK_BYTES."""
     per_seq = w.seq_len * v_local * 2.0
@@ -342,7 +374,7 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
             plan1.run("mllm_grpo_fwd_bwd", reuse_args=True)
             first["loss"] = tp.reduce_loss(first["local_loss"])  # the one exchange: a scalar all-reduce
             return first
-        parallelism = f"token-parallel dp{world}: {seqs_local} sequences per rank, scalar loss all-reduce (NCCL)"
+        parallelism = default_parallelism(world, mode, seqs_local)
         kernel = "two_pass_kernel (mllm_grpo_fwd_bwd on this rank's rows)"
     else:
         from mllm_jax_b200.vocab_parallel import VocabParallelLoss
@@ -374,9 +406,9 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
             def launch():
                 return vp.value_and_grad(*call_args, dlogits=dlogits)
             kernel = "row_stats_kernel + NCCL all-gather + combine_kernel + dlogits_kernel"
-        parallelism = f"vocab-parallel tp{world}, exchange: " + (
-            "peer stores inside the kernel" if vp_mode == "fused" else "NCCL all-gather between kernels") + (
-            f" [{vp_note}]" if vp_note else "")
+        parallelism = "sharded kernel, one shard exchanging with itself (tuning)" if job.self_exchange else \
+            default_parallelism(world, mode, seqs_local) if vp_mode == "fused" and not vp_note else (
+            f"vocab-parallel tp{world}, exchange: NCCL all-gather between kernels" + (f" [{vp_note}]" if vp_note else ""))
 
     def step():
         for _ in range(n_chunks):
@@ -477,14 +509,7 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
         "valid_tokens_per_s": value * float(data["mask"].mean().item()), "loss": loss, "device_status": status,
         "parallelism": parallelism, "roofline": roofline, "exchange": exchange, "parity": parity, "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks, "steps": steps,
-        "config": {"workload": w.name, "rows": N, "vocab": V, "global_batch": w.n_seqs, "seq_len": w.seq_len,
-                   "parallelism": parallelism,
-                   "l2": "inputs (%.1f GB per GPU per launch) exceed the 126 MB L2" % (2.0 * v_local * rows_chunk / 1e9),
-                   "chunks": None if n_chunks == 1 else
-                   f"{n_chunks} launches per step over ONE buffer of {rows_chunk} rows ({2.0 * v_local * rows_chunk / 1e9:.1f} GB "
-                   f"of logits per GPU): the full batch does not fit beside its gradient",
-                   "mask_valid_fraction": float(data["mask"].mean().item()),
-                   "epsilon": [w.epsilon_low, w.epsilon_high], "beta": w.beta, "softcap": w.softcap},
+        "config": config_dict(w, world, mode, parallelism, args.seed),
     }
     return result
 
@@ -706,6 +731,8 @@ def run_reference(args):
     from mllm_jax_b200 import synth
 
     w = synth.parse_workload(args.workload)
+    world = max(1, args.gpus)
+    mode = "single" if world == 1 else args.parallelism
     t_all = time.perf_counter()
     cb = cpu_baseline(args, w, steps=args.steps, warmup=min(args.warmup, 2))
     value = cb["value"]
@@ -713,9 +740,11 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_pass"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "sample": cb["sample"],
-                   "note": "the reference's jnp path needs JAX, which is installed neither on the build host nor on "
-                           "the GPU hosts (probed); this arm times the line-for-line torch-CPU restatement"},
+        "config": config_dict(w, world, mode, default_parallelism(world, mode, w.n_seqs // world if mode == "token"
+                                                                    else w.n_seqs), args.seed),
+        "note": "the reference's jnp path needs JAX, which is installed neither on the build host nor on the GPU hosts "
+                "(probed); this arm times the line-for-line torch-CPU restatement on a bounded sample of the same "
+                "workload (same vocabulary and distributions; the per-token cost does not depend on the row count)",
         "cpu_baseline": cb,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t_all,

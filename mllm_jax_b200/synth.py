@@ -96,6 +96,33 @@ def parse_workload(name: str) -> Workload:
     raise ValueError(f"unknown workload {name!r}: expected one of {sorted(CONFIGS)} or cfg4-<tokens>")
 
 
+def side_arrays(w: Workload, seed: int = 0):
+    """Per-token side inputs of the whole batch (small, CPU, one generator): token ids [B, T] i32, advantages [B]
+    (groups of `group` completions, Bernoulli rewards, group-normalised; an all-equal group is re-drawn), mask
+    [B, T], and the noise added to the exact log-probs for old / ref."""
+    B, T, V = w.n_seqs, w.seq_len, w.vocab
+    gs = torch.Generator(device="cpu")
+    gs.manual_seed(7 * seed + 3)
+    ids = torch.randint(0, V, (B, T), generator=gs, dtype=torch.int64).to(torch.int32)
+    adv = torch.empty(B, dtype=torch.float32)
+    for s in range(0, B, w.group):
+        n = min(w.group, B - s)
+        for _ in range(64):
+            r = (torch.rand(n, generator=gs) < w.reward_p).float()
+            if n == 1 or r.min() != r.max():
+                break
+        adv[s:s + n] = group_advantages(r, n) if n > 1 else r
+    if w.half_valid_runs:
+        # contiguous runs: the first half of every sequence-sized block is valid
+        mask = (torch.arange(T)[None, :] < T // 2).expand(B, T).float().contiguous()
+    else:
+        lens = torch.randint(w.len_lo, w.len_hi + 1, (B,), generator=gs)
+        mask = (torch.arange(T)[None, :] < lens[:, None]).float()
+    noise_old = torch.randn(B, T, generator=gs) * w.old_noise
+    noise_ref = torch.randn(B, T, generator=gs) * w.ref_noise
+    return ids, adv, mask, noise_old, noise_ref
+
+
 def make_inputs(w: Workload, seed: int = 0, device: str = "cpu", vocab_shard: Optional[tuple] = None,
                 row_shard: Optional[tuple] = None, want_logits: bool = True) -> dict:
     """Build one batch.  Returns logits [B, T, V] bf16, token_ids / mask / old / ref [B, T],
@@ -124,27 +151,7 @@ def make_inputs(w: Workload, seed: int = 0, device: str = "cpu", vocab_shard: Op
             raise ValueError(f"{B} sequences do not split over {k} ranks")
         b0, b1 = rank * (B // k), (rank + 1) * (B // k)
 
-    # side arrays of the whole batch (tiny), from one CPU generator
-    gs = torch.Generator(device="cpu")
-    gs.manual_seed(7 * seed + 3)
-    ids = torch.randint(0, V, (B, T), generator=gs, dtype=torch.int64).to(torch.int32)
-    # advantages: groups of `group` completions, Bernoulli rewards; an all-equal group is re-drawn
-    adv = torch.empty(B, dtype=torch.float32)
-    for s in range(0, B, w.group):
-        n = min(w.group, B - s)
-        for _ in range(64):
-            r = (torch.rand(n, generator=gs) < w.reward_p).float()
-            if n == 1 or r.min() != r.max():
-                break
-        adv[s:s + n] = group_advantages(r, n) if n > 1 else r
-    if w.half_valid_runs:
-        # contiguous runs: the first half of every sequence-sized block is valid
-        mask = (torch.arange(T)[None, :] < T // 2).expand(B, T).float().contiguous()
-    else:
-        lens = torch.randint(w.len_lo, w.len_hi + 1, (B,), generator=gs)
-        mask = (torch.arange(T)[None, :] < lens[:, None]).float()
-    noise_old = torch.randn(B, T, generator=gs) * w.old_noise
-    noise_ref = torch.randn(B, T, generator=gs) * w.ref_noise
+    ids, adv, mask, noise_old, noise_ref = side_arrays(w, seed)
     total_valid = float(mask.sum().item())
 
     r0, r1 = b0 * T, b1 * T  # rows of the flattened tensor this call materialises
