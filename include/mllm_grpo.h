@@ -287,7 +287,9 @@ int64_t mllm_ppo_value_workspace_bytes(int64_t n_seqs, int64_t seq_rows);
  * weight rows [vocab_start, vocab_start + vocab) with GLOBAL chosen ids; the ranks' partials, all-gathered into
  * [k * splits, n_rows, 4], go through one mllm_grpo_combine with n_shards = k * splits.
  *   hidden [n_rows, hidden_dim] bf16, rows hidden_stride elements apart;
- *   weight [vocab, hidden_dim] bf16 (one row per vocabulary entry), rows weight_stride elements apart;
+ *   weight [vocab, hidden_dim] bf16 (one row per vocabulary entry), rows weight_stride elements apart; or, with
+ *   MLLM_LM_HEAD_FLAG_WEIGHT_HV, [hidden_dim, vocab] (a flax Dense kernel as it is stored: vocabulary contiguous,
+ *   a vocabulary shard being a column range of it), read as an MN-major tensor-core operand without a transpose;
  *   hidden_dim a multiple of 64, strides multiples of 8 elements, bases 16-byte aligned, else
  *   MLLM_GRPO_ERR_UNSUPPORTED / _ALIGNMENT.  Entropy only at temperature 1 (the combine step's rule).
  * Asynchronous on the stream, allocates nothing.  A pipeline wait that runs out (never in normal
@@ -302,13 +304,14 @@ typedef struct mllm_lm_head_args {
   int64_t vocab_start;  /* global id of weight row 0 (0 unless this call holds one vocabulary shard of the head) */
   int64_t vocab_total;  /* global vocabulary size; 0 means vocab_start + vocab */
   float softcap;        /* 0 = off */
-  int32_t flags;        /* MLLM_GRPO_FLAG_SKIP_ENTROPY */
+  int32_t flags;        /* MLLM_GRPO_FLAG_SKIP_ENTROPY, MLLM_LM_HEAD_FLAG_WEIGHT_HV */
   const void* hidden;
   const void* weight;
   const int32_t* chosen_ids; /* [n_rows] */
   void* partials;            /* mllm_lm_head_partials_bytes(n_rows, vocab) bytes, 16-byte aligned */
   int32_t* device_status;    /* optional */
 } mllm_lm_head_args;
+#define MLLM_LM_HEAD_FLAG_WEIGHT_HV 256 /* weight is [hidden_dim, vocab] row-major instead of [vocab, hidden_dim] */
 int mllm_lm_head_partials(const mllm_lm_head_args* args, void* stream);
 int32_t mllm_lm_head_splits(int64_t n_rows, int64_t vocab);
 int64_t mllm_lm_head_partials_bytes(int64_t n_rows, int64_t vocab);

@@ -12,6 +12,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmllm_grpo.so"
 
 FLAG_SKIP_ENTROPY = 1
 FLAG_CE_LOSS = 2
+LM_HEAD_FLAG_WEIGHT_HV = 256
 DEV_ID_CLAMPED = 1
 DEV_WAIT_TIMEOUT = 2
 

@@ -108,7 +108,6 @@ static int validate(const mllm_grpo_args* a, unsigned need, KernelParams* k) {
   k->device_status = a->device_status;
   k->shard_rank = a->shard_rank;
   k->exchange_epoch = a->exchange_epoch;
-  k->prefetch2 = 0;
   k->peer_wait_ns = (a->peer_wait_ms > 0 ? static_cast<unsigned long long>(a->peer_wait_ms) : 2000ull) * 1000000ull;
   for (int q = 0; q < MLLM_GRPO_MAX_SHARDS; ++q) k->peer_words[q] = nullptr;
   return MLLM_GRPO_OK;

@@ -54,7 +54,6 @@ struct KernelParams {
   int shard_rank;
   int exchange_epoch;
   unsigned long long peer_wait_ns;  // limit of one wait for the other ranks' partials
-  int prefetch2;  // request the second pass's first load batch before the merge / exchange / epilogue
 };
 
 __device__ __forceinline__ float ex2f(float x) {

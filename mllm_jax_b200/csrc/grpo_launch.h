@@ -27,6 +27,11 @@ cudaError_t launch_two_pass(const KernelParams& p, int ent, bool sharded, cudaSt
 // Per-sample entropy monitors (grpo_monitors.cu).
 cudaError_t launch_entropy_stats(const float* H, const float* mask, int64_t B, int64_t T, float* ent, float* ent_win,
                                  cudaStream_t s);
+// The two kernel families behind launch_two_pass, one translation unit each.
+cudaError_t launch_two_pass_unsharded(const KernelParams& p, int ent, int cluster, int threads, int unroll, bool smem,
+                                      cudaStream_t s);
+cudaError_t launch_two_pass_sharded(const KernelParams& p, int ent, int cluster, int threads, int unroll, bool smem,
+                                    cudaStream_t s);
 // Forced plan of launch_two_pass (tuning / test hook); 0 (-1 for staged) = automatic.
 void set_two_pass_override(int cluster, int threads, int load_batch, int staged);
 

@@ -304,30 +304,10 @@ __device__ __forceinline__ float chosen_logit(const KernelParams& p, int64_t n, 
 struct EntropyGrad {
   float cot, H, lse2, inv_temp;
 };
-// The first load batch of the second pass, requested early (before the exchange and the epilogue) so that its
-// L2 latency overlaps them: the registers are those the first pass has just released.
-template <int UNROLL>
-struct FirstBatch {
-  uint4 v[UNROLL];
-  bool have;
-};
-template <int THREADS, int UNROLL, int LDX>
-__device__ __forceinline__ void load_first_batch(FirstBatch<UNROLL>& fb, const uint16_t* x16, const uint16_t* d16,
-                                                 int64_t V, uint64_t pol, bool want) {
-  const RowSplit sp(d16, V);
-  const uint4* xvec = reinterpret_cast<const uint4*>(x16 + sp.head);
-  fb.have = want && (int64_t(threadIdx.x) + int64_t(UNROLL - 1) * THREADS < sp.nvec);
-  if (fb.have) {
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) fb.v[u] = ld_row<LDX>(xvec + threadIdx.x + int64_t(u) * THREADS, pol);
-  }
-}
-
 template <int THREADS, int UNROLL, bool CAP, int LD, int LDSRC = -1, bool ENTG = false>
 __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, int64_t V, float g, float lse,
                                           int64_t cl, const SoftCap& sc, uint64_t pol,
-                                          const EntropyGrad eg = EntropyGrad{0.f, 0.f, 0.f, 1.f},
-                                          const FirstBatch<UNROLL>* first = nullptr) {
+                                          const EntropyGrad eg = EntropyGrad{0.f, 0.f, 0.f, 1.f}) {
   const int tid = threadIdx.x;
   const RowSplit sp(d16, V);  // the caller guarantees logits and dlogits rows share alignment
   uint4* dvec = reinterpret_cast<uint4*>(d16 + sp.head);
@@ -426,12 +406,6 @@ __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, in
   constexpr int LDX = LDSRC >= 0 ? LDSRC : ((LD == 0) ? 1 : LD);
   int64_t i = tid;
   constexpr int64_t kStep = int64_t(UNROLL) * THREADS;
-  if (first != nullptr && first->have) {  // this thread's first batch is already in registers
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u)
-      st_row<LD>(dvec + i + int64_t(u) * THREADS, do_vec(first->v[u], i + int64_t(u) * THREADS), pol);
-    i += kStep;
-  }
   for (; i + kStep - THREADS < sp.nvec; i += kStep) {
     uint4 v[UNROLL];
 #pragma unroll

@@ -72,9 +72,23 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
   d |= uint64_t(2) << 61;            // 128-byte swizzle
   return d;
 }
-// Instruction descriptor: D f32, A and B bf16, both K-major, N at bits 17-22 (N/8), M at bits 24-28 (M/16).
-__host__ __device__ constexpr uint32_t instr_desc(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+// The same for an MN-major operand (the weight stored [hidden, vocab], vocabulary contiguous): 64 vocabulary
+// entries (128 bytes) per row of the swizzle atom, 8 k-rows per atom (1024 bytes, the stride offset), and the
+// leading offset is the distance between two 64-entry column blocks of the tile.
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t block_bytes) {
+  uint64_t d = 0;
+  d |= uint64_t((addr & 0x3FFFFu) >> 4);
+  d |= uint64_t((block_bytes >> 4) & 0x3FFFu) << 16;  // leading byte offset: next block of 64 columns
+  d |= uint64_t(1024 >> 4) << 32;                     // stride byte offset: next group of 8 k-rows
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(2) << 61;
+  return d;
+}
+// Instruction descriptor: D f32, A and B bf16, A K-major, B K-major or MN-major (bit 16), N at bits 17-22 (N/8),
+// M at bits 24-28 (M/16).
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | (uint32_t(N >> 3) << 17) |
+         (uint32_t(M >> 4) << 24);
 }
 __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -121,6 +135,8 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   }
 }
 
+// WMN: the weight is [hidden, vocab] (vocabulary contiguous, a flax Dense kernel) instead of [vocab, hidden].
+template <bool WMN>
 __global__ void __launch_bounds__(kThreads, 1)
 lm_head_stats_kernel(const __grid_constant__ CUtensorMap map_hidden, const __grid_constant__ CUtensorMap map_weight,
                      const Params p) {
@@ -187,7 +203,14 @@ lm_head_stats_kernel(const __grid_constant__ CUtensorMap map_hidden, const __gri
           const uint32_t a_dst = tiles + uint32_t(stage) * kStageBytes, b_dst = a_dst + kABytes;
           cl::mbar_expect_tx(full_bar(stage), uint32_t(kStageBytes));
           tma_load_2d(a_dst, &map_hidden, kb * kBK, m_tile * kBM, full_bar(stage));
-          tma_load_2d(b_dst, &map_weight, kb * kBK, n0, full_bar(stage));
+          if (WMN) {
+            // four boxes of 64 vocabulary columns x 64 k-rows, 8 KB each, side by side
+#pragma unroll
+            for (int c = 0; c < kBN / 64; ++c)
+              tma_load_2d(b_dst + uint32_t(c) * (64u * kBK * 2u), &map_weight, n0 + c * 64, kb * kBK, full_bar(stage));
+          } else {
+            tma_load_2d(b_dst, &map_weight, kb * kBK, n0, full_bar(stage));
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -199,7 +222,7 @@ lm_head_stats_kernel(const __grid_constant__ CUtensorMap map_hidden, const __gri
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(kBM, kBN);
+      constexpr uint32_t idesc = instr_desc(kBM, kBN, WMN);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -215,11 +238,14 @@ lm_head_stats_kernel(const __grid_constant__ CUtensorMap map_hidden, const __gri
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_src = tiles + uint32_t(stage) * kStageBytes, b_src = a_src + kABytes;
-          const uint64_t adesc = smem_desc(a_src), bdesc = smem_desc(b_src);
+          const uint64_t adesc = smem_desc(a_src);
+          const uint64_t bdesc = WMN ? smem_desc_mn(b_src, 64u * kBK * 2u) : smem_desc(b_src);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
-            // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in the address field
-            mma_bf16(d_addr, adesc + uint64_t(2 * k), bdesc + uint64_t(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+            // K-major: 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in the address field.
+            // MN-major: 16 k-rows = two 1024-byte atoms further: +128.
+            mma_bf16(d_addr, adesc + uint64_t(2 * k), bdesc + uint64_t(WMN ? 128 * k : 2 * k), idesc,
+                     (kb | k) != 0 ? 1u : 0u);
           }
           mma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
           if (++stage == kStages) {
@@ -385,7 +411,8 @@ int mllm_lm_head_partials(const mllm_lm_head_args* a, void* stream) {
   if (a == nullptr) return MLLM_GRPO_ERR_NULL_POINTER;
   if (a->struct_size != sizeof(mllm_lm_head_args)) return MLLM_GRPO_ERR_STRUCT_SIZE;
   if (a->n_rows <= 0 || a->vocab <= 0 || a->hidden_dim <= 0) return MLLM_GRPO_ERR_BAD_SHAPE;
-  if (a->hidden_stride < a->hidden_dim || a->weight_stride < a->hidden_dim) return MLLM_GRPO_ERR_BAD_SHAPE;
+  if (a->hidden_stride < a->hidden_dim) return MLLM_GRPO_ERR_BAD_SHAPE;
+  if (a->weight_stride < ((a->flags & MLLM_LM_HEAD_FLAG_WEIGHT_HV) ? a->vocab : a->hidden_dim)) return MLLM_GRPO_ERR_BAD_SHAPE;
   if (a->vocab_start < 0 || (a->vocab_total > 0 && a->vocab_start + a->vocab > a->vocab_total)) return MLLM_GRPO_ERR_BAD_SHAPE;
   if (!a->hidden || !a->weight || !a->chosen_ids || !a->partials) return MLLM_GRPO_ERR_NULL_POINTER;
   // TMA: 16-byte aligned bases and row pitches; whole 64-element k-blocks keep the pipeline uniform
@@ -416,21 +443,31 @@ int mllm_lm_head_partials(const mllm_lm_head_args* a, void* stream) {
   if (ctas >= (int64_t(1) << 31)) return MLLM_GRPO_ERR_TOO_LARGE;
 
   CUtensorMap map_h, map_w;
-  if (!lmh::make_map(&map_h, a->hidden, a->n_rows, a->hidden_dim, a->hidden_stride, lmh::kBM) ||
-      !lmh::make_map(&map_w, a->weight, a->vocab, a->hidden_dim, a->weight_stride, lmh::kBN))
-    return MLLM_GRPO_ERR_NO_DEVICE;
+  const bool wmn = (a->flags & MLLM_LM_HEAD_FLAG_WEIGHT_HV) != 0;
+  const bool maps_ok =
+      lmh::make_map(&map_h, a->hidden, a->n_rows, a->hidden_dim, a->hidden_stride, lmh::kBM) &&
+      (wmn ? lmh::make_map(&map_w, a->weight, a->hidden_dim, a->vocab, a->weight_stride, lmh::kBK)  // [H, V]: 64 x 64 boxes
+           : lmh::make_map(&map_w, a->weight, a->vocab, a->hidden_dim, a->weight_stride, lmh::kBN));
+  if (!maps_ok) return MLLM_GRPO_ERR_NO_DEVICE;
 
   static std::once_flag attr_once[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MLLM_GRPO_ERR_NO_DEVICE;
   cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once[dev], [&] {
-    attr_err = cudaFuncSetAttribute(lmh::lm_head_stats_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(lmh::lm_head_stats_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     int(lmh::kSmemBytes));
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(lmh::lm_head_stats_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      int(lmh::kSmemBytes));
   });
   if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
-  lmh::lm_head_stats_kernel<<<unsigned(ctas), lmh::kThreads, lmh::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(
-      map_h, map_w, p);
+  if (wmn)
+    lmh::lm_head_stats_kernel<true><<<unsigned(ctas), lmh::kThreads, lmh::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(
+        map_h, map_w, p);
+  else
+    lmh::lm_head_stats_kernel<false><<<unsigned(ctas), lmh::kThreads, lmh::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(
+        map_h, map_w, p);
   count_launch();
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? MLLM_GRPO_OK : record_cuda_error(e);

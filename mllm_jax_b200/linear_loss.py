@@ -31,7 +31,7 @@ def lm_head_forward(hidden: torch.Tensor, weight: torch.Tensor, token_ids: torch
                     total_valid_token_count=None, old_per_token_logps: Optional[torch.Tensor] = None,
                     ref_per_token_logps: Optional[torch.Tensor] = None, *, cfg: Optional[LossConfig] = None,
                     workspace: Optional[torch.Tensor] = None, vocab_start: int = 0,
-                    vocab_total: Optional[int] = None, group=None) -> dict:
+                    vocab_total: Optional[int] = None, group=None, weight_layout: str = "vh") -> dict:
     """Forward of lm_head + loss without logits in HBM.
 
     tp-sharded head (lm_head kernel partitioned over "tp", MLLM_JAX/utils.py:245): pass this rank's weight rows
@@ -39,7 +39,8 @@ def lm_head_forward(hidden: torch.Tensor, weight: torch.Tensor, token_ids: torch
     per-row partials (16 bytes per row and vocabulary range) are all-gathered and merged on every rank, so all
     outputs are replicated.
 
-    hidden [B, T, H] (or [N, H]) bf16, weight [V, H] bf16 (logits = hidden @ weight.T, never stored),
+    hidden [B, T, H] (or [N, H]) bf16, weight [V, H] bf16 (logits = hidden @ weight.T, never stored) or, with
+    weight_layout="hv", [H, V] (logits = hidden @ weight: a flax Dense kernel as stored, no transpose needed),
     token_ids [B, T] aligned with the rows.  With `advantages` given the whole forward runs (loss, residuals
     lse / grad_coef for a later backward); without, only per_token_logps, token_entropy and lse are meaningful
     (the reference-model pass, train_modules/__init__.py:129-132, and plugins/training/update/ppo.py:39-43).
@@ -55,10 +56,14 @@ def lm_head_forward(hidden: torch.Tensor, weight: torch.Tensor, token_ids: torch
     if hidden.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise TypeError("hidden and weight must be bfloat16")
     B, T, H = hidden.shape
-    V = weight.shape[0]
-    if weight.shape[1] != H or hidden.stride(2) != 1 or weight.stride(1) != 1 or hidden.stride(0) != T * hidden.stride(1):
+    if weight_layout not in ("vh", "hv"):
+        raise ValueError("weight_layout must be 'vh' ([V, H]) or 'hv' ([H, V])")
+    hv = weight_layout == "hv"
+    V = weight.shape[1] if hv else weight.shape[0]
+    if weight.shape[0 if hv else 1] != H or hidden.stride(2) != 1 or weight.stride(1) != 1 or \
+            hidden.stride(0) != T * hidden.stride(1):
         raise ValueError(f"hidden {tuple(hidden.shape)} / weight {tuple(weight.shape)}: need [B, T, H] rows evenly "
-                         "spaced and [V, H], both with unit stride along H")
+                         "spaced and a [V, H] (or [H, V]) weight with unit stride along its last dimension")
     if cfg.temperature != 1.0 and cfg.compute_entropy:
         raise ValueError("the entropy of the folded forward needs temperature 1 (pass compute_entropy=False)")
     dev = hidden.device
@@ -83,7 +88,7 @@ def lm_head_forward(hidden: torch.Tensor, weight: torch.Tensor, token_ids: torch
     a.hidden_stride, a.weight_stride = hidden.stride(1), weight.stride(0)
     a.vocab_start, a.vocab_total = int(vocab_start), int(vocab_total) if vocab_total is not None else int(vocab_start) + V
     a.softcap = float(cfg.softcap) if cfg.softcap else 0.0
-    a.flags = 0 if cfg.compute_entropy else _lib.FLAG_SKIP_ENTROPY
+    a.flags = (0 if cfg.compute_entropy else _lib.FLAG_SKIP_ENTROPY) | (_lib.LM_HEAD_FLAG_WEIGHT_HV if hv else 0)
     a.hidden, a.weight = hidden.data_ptr(), weight.data_ptr()
     a.chosen_ids, a.partials = prob.chosen_ids.data_ptr(), workspace.data_ptr()
     a.device_status = prob.device_status.data_ptr()

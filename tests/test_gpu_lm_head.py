@@ -39,11 +39,17 @@ def _case(B, T, H, V, seed, scale=0.5, **kw):
     (1, 130, 128, 10240),    # 40 vocabulary tiles: three splits, accumulator ping-pong inside a CTA
     (3, 50, 896, 4099),      # vocabulary not a multiple of 8, Qwen2.5-0.5B's hidden size
 ])
-def test_folded_forward_matches_oracle(cuda, B, T, H, V):
+@pytest.mark.parametrize("layout", ["vh", "hv"])
+def test_folded_forward_matches_oracle(cuda, B, T, H, V, layout):
+    """layout "vh": weight [V, H] (K-major operand); "hv": weight [H, V] as a flax Dense kernel stores it
+    (MN-major operand, needs a vocabulary that is a multiple of 8 for TMA's 16-byte row pitch)."""
+    if layout == "hv" and V % 8:
+        pytest.skip("[H, V] weights need V % 8 == 0")
     hidden, weight, ids, mask, adv, nv, old, ref_lp, oin, shifted = _case(B, T, H, V, seed=300 + H)
     ref = O.reference_call(shifted, oin, beta=0.04, dtype=torch.float64)
-    out = lm_head_forward(hidden.to(cuda), weight.to(cuda), ids.to(cuda), mask.to(cuda), adv.to(cuda), nv,
-                          old.to(cuda), ref_lp.to(cuda), cfg=G.LossConfig(beta=0.04))
+    w_dev = weight.to(cuda) if layout == "vh" else weight.t().contiguous().to(cuda)
+    out = lm_head_forward(hidden.to(cuda), w_dev, ids.to(cuda), mask.to(cuda), adv.to(cuda), nv,
+                          old.to(cuda), ref_lp.to(cuda), cfg=G.LossConfig(beta=0.04), weight_layout=layout)
     torch.cuda.synchronize()
     assert G.ops.check_device_status(out["problem"]) == 0
     assert (out["per_token_logps"].cpu().double() - ref["per_token_logps"]).abs().max() <= LP_ATOL
@@ -78,6 +84,22 @@ def test_folded_forward_only_logprobs(cuda):
     out = lm_head_forward(hidden.to(cuda), weight.to(cuda), ids.to(cuda))
     torch.cuda.synchronize()
     assert (out["per_token_logps"].cpu().double() - lp).abs().max() <= LP_ATOL
+
+
+def test_folded_forward_hv_weight_shard(cuda):
+    """A vocabulary shard of an [H, V] weight is a column range of it (no copy): strided rows, global ids."""
+    B, T, H, V = 1, 140, 128, 2048
+    hidden, weight, ids, mask, adv, nv, old, ref_lp, oin, shifted = _case(B, T, H, V, seed=92)
+    lp_ref = torch.log_softmax(shifted[:, :-1], -1).gather(-1, ids.long()[..., None])[..., 0]
+    w_hv = weight.t().contiguous().to(cuda)  # [H, V]
+    full = lm_head_forward(hidden.to(cuda), w_hv, ids.to(cuda), weight_layout="hv")
+    assert (full["per_token_logps"].cpu().double() - lp_ref).abs().max() <= LP_ATOL
+    # the upper half of the vocabulary alone: every chosen id below 1024 belongs to "another shard"
+    upper = lm_head_forward(hidden.to(cuda), w_hv[:, 1024:], ids.to(cuda), weight_layout="hv", vocab_start=1024,
+                            vocab_total=V)
+    torch.cuda.synchronize()
+    lse_upper = torch.logsumexp(shifted[:, :-1, 1024:], -1)
+    assert (upper["lse"].cpu().double() - lse_upper).abs().max() <= LP_ATOL
 
 
 def test_folded_forward_rejects_what_it_cannot_run(cuda):
