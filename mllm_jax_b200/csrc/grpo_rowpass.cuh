@@ -200,10 +200,26 @@ __device__ __forceinline__ RowStats row_pass1(const uint16_t* row16, int64_t V, 
     for (int u = 0; u < UNROLL; ++u) v[u] = ld_row<LD>(vec + i + int64_t(u) * THREADS, pol);
     fold_vectors<ENT, CAP, UNROLL>(acc, v, inv_temp, k2, sc);
   }
-  for (; i < sp.nvec; i += THREADS) {
-    uint4 v[1];
-    v[0] = ld_row<LD>(vec + i, pol);
-    fold_vectors<ENT, CAP, 1>(acc, v, inv_temp, k2, sc);
+  if constexpr (UNROLL > 8) {  // batches of 10 are only chosen where next to nothing is left over
+    for (; i < sp.nvec; i += THREADS) {
+      uint4 v[1];
+      v[0] = ld_row<LD>(vec + i, pol);
+      fold_vectors<ENT, CAP, 1>(acc, v, inv_temp, k2, sc);
+    }
+  } else if (UNROLL > 1 && i < sp.nvec) {
+    // Tail (fewer than UNROLL vectors left for this thread): all of them requested at once, one latency
+    // period instead of one per vector, then folded one by one so that nothing is computed on padding.
+    uint4 v[UNROLL - 1];
+#pragma unroll
+    for (int u = 0; u < UNROLL - 1; ++u)
+      if (i + int64_t(u) * THREADS < sp.nvec) v[u] = ld_row<LD>(vec + i + int64_t(u) * THREADS, pol);
+#pragma unroll
+    for (int u = 0; u < UNROLL - 1; ++u) {
+      if (i + int64_t(u) * THREADS < sp.nvec) {
+        const uint4 one[1] = {v[u]};
+        fold_vectors<ENT, CAP, 1>(acc, one, inv_temp, k2, sc);
+      }
+    }
   }
   // Block reduction with ONE barrier: warps merge (m, s, u) by shuffles, lane 0 parks the warp's
   // result in shared memory, and after the barrier every warp merges the per-warp entries again by
@@ -414,9 +430,20 @@ __device__ __forceinline__ void row_pass2(const uint16_t* x16, uint16_t* d16, in
     for (int u = 0; u < UNROLL; ++u)
       st_row<LD>(dvec + i + int64_t(u) * THREADS, do_vec(v[u], i + int64_t(u) * THREADS), pol);
   }
-  for (; i < sp.nvec; i += THREADS) {
-    const uint4 v = ld_row<LDX>(xvec + i, pol);
-    st_row<LD>(dvec + i, do_vec(v, i), pol);
+  if constexpr (UNROLL > 8) {
+    for (; i < sp.nvec; i += THREADS) {
+      const uint4 v = ld_row<LDX>(xvec + i, pol);
+      st_row<LD>(dvec + i, do_vec(v, i), pol);
+    }
+  } else if (UNROLL > 1 && i < sp.nvec) {  // tail: every remaining load in flight at once
+    uint4 v[UNROLL - 1];
+#pragma unroll
+    for (int u = 0; u < UNROLL - 1; ++u)
+      if (i + int64_t(u) * THREADS < sp.nvec) v[u] = ld_row<LDX>(xvec + i + int64_t(u) * THREADS, pol);
+#pragma unroll
+    for (int u = 0; u < UNROLL - 1; ++u)
+      if (i + int64_t(u) * THREADS < sp.nvec)
+        st_row<LD>(dvec + i + int64_t(u) * THREADS, do_vec(v[u], i + int64_t(u) * THREADS), pol);
   }
 }
 

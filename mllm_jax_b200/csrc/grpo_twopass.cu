@@ -20,31 +20,50 @@ cudaError_t launch_two_pass_unsharded(const KernelParams& p, int ent, int cluste
   return launch_two_pass_family<false>(p, ent, cluster, threads, unroll, smem, s);
 }
 
-// Cluster size, thread count and load-batch size for a row of `vocab` columns: slices of roughly 32-48 KB.
+// Cluster size, thread count and load-batch size for a row of `vocab` columns.  Measured on one B200, 32768
+// rows, ms per step (unsplit 256 threads / 2 CTAs x 128 / 4 CTAs x 128): 64 KB rows 0.673 / 0.827 / 1.133,
+// 76 KB 0.821 / 0.893 / 1.147, 100 KB 1.129 / 1.134 / 1.323, 125 KB 1.523 / 1.469 / 1.723,
+// 148 KB 1.875 / 1.731 / 1.790, 195 KB 2.554 / 2.398 / 2.252.
 void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, int* threads, bool* smem, int* unroll) {
   const int64_t row_bytes = p.vocab * 2;
-  int cl = row_bytes >= 96 * 1024 ? 4 : (row_bytes >= 56 * 1024 ? 2 : 1);
+  int cl = row_bytes >= 176 * 1024 ? 4 : (row_bytes >= 112 * 1024 ? 2 : 1);
   int un = 8;
   if (cl > 1) {
-    // A thread of a 128-thread CTA loads its slice in batches of `un` 16-byte vectors and finishes with a
-    // one-vector-at-a-time remainder loop, which has little memory parallelism.  Take the split (8 or 4 CTAs
-    // for rows of 192 KB and more) and the batch size that leave the smallest share to that loop; the soft-cap
-    // kernels need too many registers for batches of 10.  Measured on one B200, batch 8 -> chosen:
-    // V=151936: 3.49 -> 3.44 ms (8 CTAs, batches of 6); V=128256: 12.34 -> 11.60 ms (4 CTAs, batches of 10);
-    // V=256000 with soft-cap: 15.99 -> 15.11 ms (batches of 6; 8 and 4 CTAs alike).
+    // A thread of a 128-thread CTA loads its slice in batches of `un` 16-byte vectors; what is left over
+    // (fewer than `un` vectors) is requested at once and folded vector by vector, except with batches of
+    // 10, whose leftovers go one at a time (the tail buffers cost that kernel registers).  So: batches of
+    // 10 where they leave under 5 % over, else batches of 8, on the coarser split (8 or 4 CTAs for rows of
+    // 192 KB and more).  Measured on one B200: V=151936 4 CTAs x 8: 3.43 ms (8 CTAs x 6: 3.48; 4 x 10: 3.52);
+    // V=128256 4 CTAs x 10: 11.6 ms (4 x 6: 11.9, 4 x 8: 12.1, 8 x 6: 12.2).  The soft-cap kernels need too
+    // many registers for batches of 10 and take the (split, 8 or 6) pair with the smallest leftover share:
+    // V=256000: 8 CTAs x 6 15.1 ms, 4 x 6 15.1, 4 x 8 15.6, 8 x 8 16.8.
     const bool cap = p.softcap > 0.f;
-    double best = 2.0;
     const int c_hi = row_bytes >= 192 * 1024 ? 8 : cl, c_lo = row_bytes >= 192 * 1024 ? 4 : cl;
-    for (int c = c_hi; c >= c_lo; c /= 2) {
+    auto leftover = [&](int c, int u) {
       const double n = double((p.vocab / 8 + c - 1) / c) / 128.0;
-      for (int u = cap ? 8 : 10; u >= 6; u -= 2) {
-        const double singles = (n - double(u) * double(int64_t(n / double(u)))) / n;
-        if (singles < best - 0.02) {
-          best = singles;
-          cl = c;
-          un = u;
+      return (n - double(u) * double(int64_t(n / double(u)))) / n;
+    };
+    if (cap) {
+      double best = 2.0;
+      for (int c = c_hi; c >= c_lo; c /= 2) {
+        for (int u = 8; u >= 6; u -= 2) {
+          const double share = leftover(c, u);
+          if (share < best - 0.02) {
+            best = share;
+            cl = c;
+            un = u;
+          }
         }
       }
+    } else if (leftover(c_lo, 10) < 0.05) {
+      cl = c_lo;
+      un = 10;
+    } else if (leftover(c_hi, 10) < 0.05) {
+      cl = c_hi;
+      un = 10;
+    } else {
+      cl = c_lo;
+      un = 8;
     }
   }
   // With the exchange in the kernel every CTA sits through one store -> visible -> poll round trip (1-2 us)
@@ -65,7 +84,7 @@ void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, i
     if (!aligned16 || ent == 2 || nvec - (cl - 1) * per <= 0 || p.n_seqs * p.seq_rows * cl >= (int64_t(1) << 31)) cl = 1;
   }
   // measured on one B200 (unsplit rows): 38 KB rows 64 threads, 76 KB 256, 152 KB and longer 512
-  int th = f_th > 0 ? f_th : (cl > 1 ? 128 : (row_bytes < 56 * 1024 ? 64 : (row_bytes < 112 * 1024 || sharded ? 256 : 512)));
+  int th = f_th > 0 ? f_th : (cl > 1 ? 128 : (row_bytes < 48 * 1024 ? 64 : (row_bytes < 112 * 1024 || sharded ? 256 : 512)));
   // Rows of at most 48 KB that are not split: stage the row in shared memory with one bulk (TMA) copy
   // and run both passes from there (38 KB rows on one B200: 0.400 ms against 0.452 ms through
   // registers).  Longer rows and cluster slices measured slower that way (too few CTAs per SM).
