@@ -601,8 +601,8 @@ def main():
         torch.cuda.empty_cache()
         try:
             f = run_fold_lm_head(job, args, steps=3, warmup=3)
-            fold = {k: f[k] for k in ("metric", "value", "ms_per_step", "config", "roofline", "library_path", "parity",
-                                      "device_status")}
+            fold = {k: f[k] for k in ("metric", "value", "ms_per_step", "config", "roofline", "library_path", "weight_hv",
+                                      "parity", "device_status")}
         except torch.OutOfMemoryError as exc:
             fold = {"skipped": f"out of device memory ({str(exc)[:60]})"}
     cpu = None
@@ -686,6 +686,11 @@ def run_fold_lm_head(job, args, steps, warmup):
     launches = _lib.launch_count() - launches0
     clocks = sampler.stop()
     ms_lib, out_lib = timed(library, max(3, steps // 2), 3)
+    # the same forward on the weight as a flax Dense kernel stores it ([H, V], MN-major tensor-core operand)
+    w_hv = weight.t().contiguous()
+    ms_hv, out_hv = timed(lambda: lm_head_forward(hidden, w_hv, *call[2:], cfg=cfg, workspace=work, weight_layout="hv"),
+                          max(3, steps // 2), 3)
+    hv_lp_diff = float((out_hv["per_token_logps"] - lm_head_forward(*call, cfg=cfg)["per_token_logps"]).abs().max().item())
     flops = 2.0 * N * V * H
     peak = float(job.peaks.get("bf16_tflops_sustained", 1400.0))
     tf = flops / (ms_fused * 1e-3) / 1e12
@@ -714,6 +719,8 @@ def run_fold_lm_head(job, args, steps, warmup):
                      " (library bf16 GEMM sustained)", "flops_per_launch": flops, "ms_per_launch": ms_fused,
                      "traffic": None,
                      "note": "ms_per_launch covers the tensor-core kernel plus the two small merge kernels"},
+        "weight_hv": {"what": "same kernel on the [hidden, vocab] weight (MN-major operand, no transpose)",
+                      "ms_per_step": ms_hv, "tflops": flops / (ms_hv * 1e-3) / 1e12, "lp_abs_vs_vh": hv_lp_diff},
         "library_path": {"what": "torch.matmul (library GEMM) writing bf16 logits + mllm_grpo_fwd reading them",
                          "ms_per_step": ms_lib, "tflops": flops / (ms_lib * 1e-3) / 1e12,
                          "logits_bytes": 2.0 * N * V, "loss": float(out_lib["loss"].item())},

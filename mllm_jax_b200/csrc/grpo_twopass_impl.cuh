@@ -144,11 +144,14 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
     slots[0] = make_float4(st.M, st.S, st.U, yc_own);
   }
 
+  TokenSide side = {};
   if (SHARDED) {
     const int k = p.n_shards, me = p.shard_rank;
     const int64_t N = p.n_seqs * p.scored_rows;
     const int64_t half = int64_t(p.exchange_epoch & 1) * int64_t(k) * N;  // parity half of every buffer
     if (CL == 1) __syncthreads();                                          // slots[0] visible to threads < k
+    // The epilogue's side inputs are requested now, so that their latency runs beside the exchange's.
+    if (tid == 0) side = load_token_side(p, n, b);
     if (tid < k) {
       if (rank == 0) {  // one CTA per row talks to the other GPUs
         const float4 mine = merge_partials(slots, CL);
@@ -196,7 +199,7 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
     all.U = m.z;
     all.S2 = st.S2;  // temperature != 1 entropy exists only unsplit (CL == 1, not sharded)
     all.U2 = st.U2;
-    TokenOut o = token_epilogue<ENT>(p, n, b, all, m.w);
+    TokenOut o = SHARDED ? token_epilogue_core<ENT>(p, all, m.w, side) : token_epilogue<ENT>(p, n, b, all, m.w);
     if (SHARDED && peer_lost) {  // merged stale words: make the row unusable instead of silently wrong
       o.lp = o.entropy = o.loss_term = __int_as_float(0x7fc00000);
       o.grad_coef = 0.f;

@@ -63,6 +63,20 @@ def _run_rank(rank, world, port, ret):
             assert (out["token_entropy"].cpu() - ref["token_entropy"]).abs().max() <= ENT_ATOL, name
             assert_loss_close(out["loss"].item(), ref["loss"].item(), what=name)
             assert_dlogits_close(out["dlogits"], want_d, what=name)
+        # soft-capped logits through the fused path (staged shards compute their exponentials during the exchange)
+        big, big_in = make_case(B, L, V, seed=96, old="wide", ref=True, sigma=6.0)
+        cap_attrs = dict(beta=0.04, epsilon_low=0.2, epsilon_high=0.3, softcap=30.0)
+        ref_c = O.reference_value_and_grad(big, big_in, **cap_attrs)
+        vpc = VocabParallelLoss(V, G.LossConfig(**cap_attrs))
+        dc = to_device(big_in, dev)
+        sh = big[:, :-1, vp.start:vp.stop].contiguous().to(dev)
+        oc = vpc.value_and_grad_fused(sh, dc["input_ids"][:, 1:], dc["labels"][:, 1:], dc["advantages"],
+                                      dc["total_valid_token_count"], dc["old_per_token_logps"],
+                                      dc["ref_per_token_logps"], dlogits=torch.empty_like(sh))
+        torch.cuda.synchronize()
+        assert (oc["per_token_logps"].cpu() - ref_c["per_token_logps"]).abs().max() <= LP_ATOL
+        assert_loss_close(oc["loss"].item(), ref_c["loss"].item(), what="fused soft-cap")
+        assert_dlogits_close(oc["dlogits"], ref_c["dlogits"][:, :-1, vp.start:vp.stop], what="fused soft-cap")
         if world > 1:
             # tp-sharded lm_head folded into the forward: every rank multiplies by its own weight rows, the
             # per-row partials are all-gathered (16 bytes per row and vocabulary range) and merged on every rank
