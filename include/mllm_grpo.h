@@ -321,7 +321,7 @@ int64_t mllm_grpo_workspace_bytes(int64_t n_tokens);
 
 /* Tuning / test hook: forces how mllm_grpo_fwd_bwd and mllm_grpo_fwd_bwd_sharded run in this process, until
  * called again.  sweeps != 0: mllm_grpo_fwd_bwd takes the separate forward and backward kernels.  cluster
- * (1/2/4/8 CTAs per row), threads (64/128/256/512 per CTA), load_batch (6/8/10 vectors per thread) and staged
+ * (1/2/4/6/8 CTAs per row), threads (64/128/256/512 per CTA), load_batch (6/8/10 vectors per thread) and staged
  * (0/1: row shard held in shared memory) override the plan the library derives from the row length; 0 (-1 for
  * staged) leaves a field automatic.  Combinations a kernel cannot run fall back to the nearest one that it can.
  * Production code never needs this: the automatic plan is the measured one. */

@@ -297,6 +297,9 @@ cudaError_t launch_c(const KernelParams& p, int ent, int cluster, int threads, i
     case 1: return launch_t<1, SHARDED>(p, ent, threads, unroll, smem, s);
     case 2: return launch_t<2, SHARDED>(p, ent, threads, unroll, smem, s);
     case 4: return launch_t<4, SHARDED>(p, ent, threads, unroll, smem, s);
+    case 6:
+      if constexpr (!SHARDED) return launch_t<6, SHARDED>(p, ent, threads, unroll, smem, s);
+      return launch_t<4, SHARDED>(p, ent, threads, unroll, smem, s);
     default: return launch_t<8, SHARDED>(p, ent, threads, unroll, smem, s);
   }
 }
