@@ -602,7 +602,7 @@ def main():
         gc.collect()
         torch.cuda.empty_cache()
         try:
-            f = run_fold_lm_head(job, args, steps=3, warmup=3)
+            f = run_fold_lm_head(job, args, steps=5, warmup=5)
             fold = {k: f[k] for k in ("metric", "value", "ms_per_step", "config", "roofline", "library_path", "weight_hv",
                                       "parity", "device_status")}
         except torch.OutOfMemoryError as exc:
