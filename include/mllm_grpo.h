@@ -108,8 +108,10 @@ typedef struct mllm_grpo_args {
   void* dlogits;          /* bf16 [n_seqs, seq_rows, row_stride]; may alias logits (in place) */
 
   /* ---- vocabulary-sharded path ---- */
-  float* partials;        /* [B*T, 4] (max, sumexp, sum e*y, chosen-or-0) of THIS shard */
-  const float* gathered_partials; /* [n_shards, B*T, 4]: every shard's partials (after the exchange) */
+  float* partials;        /* [B*T, 4] (max, sumexp, sum e*y, chosen-or-0) of THIS shard; [B*T, 6] when the entropy
+                             is requested at temperature != 1 (then: max, sumexp, 0, chosen-or-0, and the two sums
+                             of the entropy on y/temperature) */
+  const float* gathered_partials; /* [n_shards, B*T, 4 or 6]: every shard's partials (after the exchange) */
   int32_t n_shards;
   int32_t shard_rank;     /* this call's shard index in [0, n_shards) (peer-exchange entry point only) */
 
@@ -174,14 +176,19 @@ int mllm_grpo_fwd_bwd(const mllm_grpo_args* args, void* stream);
 int mllm_grpo_scale_grad(const mllm_grpo_args* args, void* stream);
 
 /* Vocabulary-sharded forward, step 1: per-token (max, sumexp, sum e*y,
- * chosen-logit-or-0) of this shard's columns -> partials[B*T, 4].  This is the
+ * chosen-logit-or-0) of this shard's columns -> partials[B*T, 4] (6 floats per token when the entropy is wanted
+ * at temperature != 1: mllm_grpo_partial_width tells which).  This is the
  * per-shard part of the all-reduce(max)/all-reduce(sum) XLA inserts when
  * log_softmax runs on tp-sharded logits (MLLM_JAX/utils.py:245). */
 int mllm_grpo_fwd_partials(const mllm_grpo_args* args, void* stream);
 
-/* Vocabulary-sharded forward, step 2: merge gathered_partials[n_shards, B*T, 4]
+/* Vocabulary-sharded forward, step 2: merge gathered_partials[n_shards, B*T, width]
  * and run the per-token epilogue; same outputs as mllm_grpo_fwd. */
 int mllm_grpo_combine(const mllm_grpo_args* args, void* stream);
+
+/* Floats per token in partials / gathered_partials for these attributes: 6 when token_entropy is requested
+ * (non-NULL, no SKIP_ENTROPY flag) at temperature != 1, else 4. */
+int32_t mllm_grpo_partial_width(const mllm_grpo_args* args);
 
 /* Vocabulary-sharded forward AND backward in one kernel per GPU, with the exchange inside it.
  * Each rank (one process per GPU) calls it on its own column shard at the same time.  A CTA

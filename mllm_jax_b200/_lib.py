@@ -22,7 +22,7 @@ EXPORTS = (
     "mllm_grpo_last_cuda_error", "mllm_grpo_launch_count", "mllm_grpo_fwd_static_scratch",
     "mllm_grpo_fwd_bwd_sharded", "mllm_grpo_exchange_bytes", "mllm_grpo_set_plan_override",
     "mllm_grpo_entropy_stats", "mllm_grpo_scale_grad", "mllm_ppo_value_loss", "mllm_ppo_value_workspace_bytes",
-    "mllm_lm_head_partials", "mllm_lm_head_splits", "mllm_lm_head_partials_bytes",
+    "mllm_lm_head_partials", "mllm_lm_head_splits", "mllm_lm_head_partials_bytes", "mllm_grpo_partial_width",
 )
 
 
@@ -106,6 +106,8 @@ def load():
         fn.restype = C.c_int
     lib.mllm_ppo_value_loss.argtypes = [C.POINTER(PpoValueArgs), C.c_void_p]
     lib.mllm_ppo_value_loss.restype = C.c_int
+    lib.mllm_grpo_partial_width.argtypes = [C.POINTER(GrpoArgs)]
+    lib.mllm_grpo_partial_width.restype = C.c_int32
     lib.mllm_lm_head_partials.argtypes = [C.POINTER(LmHeadArgs), C.c_void_p]
     lib.mllm_lm_head_partials.restype = C.c_int
     lib.mllm_lm_head_splits.argtypes = [C.c_int64, C.c_int64]

@@ -194,8 +194,8 @@ int mllm_grpo_fwd_partials(const mllm_grpo_args* args, void* stream) {
   KernelParams k;
   int st = validate(args, kLogits | kIds | kPartialsOut, &k);
   if (st) return st;
-  int ent = (args->flags & MLLM_GRPO_FLAG_SKIP_ENTROPY) ? 0 : 1;
-  if (ent && args->temperature != 1.0f) return MLLM_GRPO_ERR_UNSUPPORTED;  // sharded entropy needs temperature 1
+  // entropy at temperature != 1: records of 6 floats (two more sums on y/temperature), see the header
+  const int ent = args->temperature == 1.0f ? ((args->flags & MLLM_GRPO_FLAG_SKIP_ENTROPY) ? 0 : 1) : entropy_mode(args);
   cudaError_t e = launch_row_stats(k, 1, ent, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail_cuda(e);
   return MLLM_GRPO_OK;
@@ -205,14 +205,18 @@ int mllm_grpo_combine(const mllm_grpo_args* args, void* stream) {
   KernelParams k;
   int st = validate(args, kEpilogueIn | kEpilogueOut | kGathered, &k);
   if (st) return st;
-  int ent = entropy_mode(args);
-  if (ent == 2) return MLLM_GRPO_ERR_UNSUPPORTED;
+  const int ent = entropy_mode(args);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e = launch_combine(k, ent, s);
   if (e != cudaSuccess) return fail_cuda(e);
   e = launch_loss_reduce(k, s);
   if (e != cudaSuccess) return fail_cuda(e);
   return MLLM_GRPO_OK;
+}
+
+int32_t mllm_grpo_partial_width(const mllm_grpo_args* args) {
+  if (args == nullptr) return 4;
+  return entropy_mode(args) == 2 ? 6 : 4;
 }
 
 int mllm_grpo_entropy_stats(const mllm_grpo_args* args, void* stream) {

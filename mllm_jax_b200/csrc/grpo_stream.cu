@@ -36,8 +36,18 @@ __global__ void __launch_bounds__(THREADS) row_stats_kernel(const KernelParams p
     int64_t cl;
     const float yc = chosen_logit<CAP>(p, n, row16, sc, &mine, &cl);
     if (MODE == 1) {
-      float4 out = make_float4(st.M, st.S, st.U, mine ? yc : 0.f);
-      reinterpret_cast<float4*>(p.partials)[n] = out;
+      if (ENT == 2) {
+        // temperature != 1 with the entropy: two more sums, on y/temperature (records of 6 floats)
+        float* rec = p.partials + n * 6;
+        rec[0] = st.M;
+        rec[1] = st.S;
+        rec[2] = 0.f;
+        rec[3] = mine ? yc : 0.f;
+        rec[4] = st.S2;
+        rec[5] = st.U2;
+      } else {
+        reinterpret_cast<float4*>(p.partials)[n] = make_float4(st.M, st.S, st.U, mine ? yc : 0.f);
+      }
     } else if (MODE == 2) {
       const float lse = st.M + logf(st.S);
       p.per_token_logps[n] = (yc - lse) * inv_temp;
@@ -59,15 +69,17 @@ __global__ void __launch_bounds__(THREADS) row_stats_kernel(const KernelParams p
   }
 }
 
-// Merge the shards' partials (max, sumexp, sum e*y, chosen) and run the epilogue.
+// Merge the shards' partials (max, sumexp, sum e*y, chosen; for ENT == 2 also the two sums on y/temperature,
+// records of 6 floats) and run the epilogue.
 template <int ENT>
 __global__ void __launch_bounds__(256) combine_kernel(const KernelParams p) {
   const int64_t N = p.n_seqs * p.scored_rows;
   const int64_t n = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
   if (n >= N) return;
-  const float4* g = reinterpret_cast<const float4*>(p.gathered_partials);
+  constexpr int W = ENT == 2 ? 6 : 4;
+  const float* g = p.gathered_partials;
   float M = kNegInit;
-  for (int r = 0; r < p.n_shards; ++r) M = fmaxf(M, g[int64_t(r) * N + n].x);
+  for (int r = 0; r < p.n_shards; ++r) M = fmaxf(M, g[(int64_t(r) * N + n) * W]);
   RowStats st;
   st.M = M;
   st.S = 0.f;
@@ -76,11 +88,17 @@ __global__ void __launch_bounds__(256) combine_kernel(const KernelParams p) {
   st.U2 = 0.f;
   float yc = 0.f;
   for (int r = 0; r < p.n_shards; ++r) {
-    const float4 q = g[int64_t(r) * N + n];
-    const float scl = ex2f((q.x - M) * kLog2e);
-    st.S = fmaf(q.y, scl, st.S);
-    st.U = fmaf(q.z, scl, st.U);
-    yc += q.w;
+    const float* q = g + (int64_t(r) * N + n) * W;
+    const float d = (q[0] - M) * kLog2e;
+    const float scl = ex2f(d);
+    st.S = fmaf(q[1], scl, st.S);
+    st.U = fmaf(q[2], scl, st.U);
+    yc += q[3];
+    if (ENT == 2) {
+      const float scl2 = ex2f(d * p.inv_temperature);
+      st.S2 = fmaf(q[4], scl2, st.S2);
+      st.U2 = fmaf(q[5], scl2, st.U2);
+    }
   }
   const int64_t b = n / p.scored_rows;
   const TokenOut o = token_epilogue<ENT>(p, n, b, st, yc);
@@ -230,8 +248,10 @@ cudaError_t launch_combine(const KernelParams& p, int ent, cudaStream_t s) {
   const unsigned grid = static_cast<unsigned>((N + 255) / 256);
   if (ent == 0)
     combine_kernel<0><<<grid, 256, 0, s>>>(p);
-  else
+  else if (ent == 1)
     combine_kernel<1><<<grid, 256, 0, s>>>(p);
+  else
+    combine_kernel<2><<<grid, 256, 0, s>>>(p);
   count_launch();
   return cudaGetLastError();
 }

@@ -26,9 +26,10 @@ def shard_bounds(vocab_total: int, rank: int, world: int) -> tuple[int, int]:
 
 
 def exchange_partials(partials: torch.Tensor, group=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """All-gather the per-rank partials [N, 4] into [world, N, 4] (rank-major), on any backend."""
-    if partials.dim() != 2 or partials.shape[1] != 4:
-        raise ValueError(f"partials must be [N, 4], got {tuple(partials.shape)}")
+    """All-gather the per-rank partials [N, 4] (or [N, 6]: entropy at temperature != 1) into [world, N, width]
+    (rank-major), on any backend."""
+    if partials.dim() != 2 or partials.shape[1] not in (4, 6):
+        raise ValueError(f"partials must be [N, 4] or [N, 6], got {tuple(partials.shape)}")
     world = dist.get_world_size(group)
     if out is None:
         out = torch.empty(world, *partials.shape, dtype=partials.dtype, device=partials.device)
@@ -100,9 +101,11 @@ class VocabParallelLoss:
         p = TokenLossProblem(shard_logits, token_ids, mask, advantages, total_valid, old_logps, ref_logps, self.cfg,
                              scored_rows=T, vocab=self.stop - self.start, vocab_start=self.start,
                              vocab_total=self.vocab_total)
-        if self._partials is None or self._partials.shape[0] != p.N:
-            self._partials = torch.empty(p.N, 4, dtype=torch.float32, device=shard_logits.device)
-            self._gathered = torch.empty(self.world, p.N, 4, dtype=torch.float32, device=shard_logits.device)
+        # 4 floats per token, 6 when the entropy is wanted at temperature != 1 (two more sums on y/temperature)
+        width = 6 if (self.cfg.compute_entropy and self.cfg.temperature != 1.0) else 4
+        if self._partials is None or self._partials.shape != (p.N, width):
+            self._partials = torch.empty(p.N, width, dtype=torch.float32, device=shard_logits.device)
+            self._gathered = torch.empty(self.world, p.N, width, dtype=torch.float32, device=shard_logits.device)
         p.partials, p.gathered, p.n_shards = self._partials, self._gathered, self.world
         return p
 
@@ -172,7 +175,12 @@ class VocabParallelLoss:
                              scored_rows: Optional[int] = None) -> dict:
         """Same result as value_and_grad through ONE kernel per GPU (mllm_grpo_fwd_bwd_sharded): the
         per-token partials cross NVLink as peer stores issued by the kernel itself, and the row shard
-        is re-read from L2 for the backward.  All ranks must call it the same number of times."""
+        is re-read from L2 for the backward.  All ranks must call it the same number of times.
+        The entropy at temperature != 1 needs two more sums per shard than the kernel's exchange record carries:
+        that combination takes the all-gather path (value_and_grad) instead."""
+        if self.cfg.compute_entropy and self.cfg.temperature != 1.0:
+            return self.value_and_grad(shard_logits, token_ids, mask, advantages, total_valid, old_logps, ref_logps,
+                                       dlogits)
         return self.step_fused(self.plan_fused(shard_logits, token_ids, mask, advantages, total_valid, old_logps,
                                                ref_logps, dlogits, grad_scale, scored_rows))
 

@@ -288,10 +288,13 @@ def analytic_rows(x: np.ndarray, chosen: np.ndarray, mask: np.ndarray, adv: np.n
     return out
 
 
-def shard_partials(x: np.ndarray, chosen: np.ndarray, vocab_start: int, softcap: Optional[float] = None) -> np.ndarray:
+def shard_partials(x: np.ndarray, chosen: np.ndarray, vocab_start: int, softcap: Optional[float] = None,
+                   temperature: Optional[float] = None) -> np.ndarray:
     """(max, sumexp, sum e*y, chosen-or-0) of a column shard x [n, Vs] in float64: what one
     vocabulary shard contributes before the cross-shard max / sum (the collectives XLA inserts
-    for log_softmax over tp-sharded logits, MLLM_JAX/utils.py:245)."""
+    for log_softmax over tp-sharded logits, MLLM_JAX/utils.py:245).  With a temperature other than 1 the record
+    has six entries: (max, sumexp, 0, chosen-or-0, sum e2, sum e2*y) with e2 = e^((y - max)/temperature), the sums
+    the entropy of softmax(y / temperature) needs (train_modules/__init__.py:136-138)."""
     x = np.asarray(x, dtype=np.float64)
     y = softcap * np.tanh(x / softcap) if softcap else x
     M = y.max(axis=1)
@@ -299,6 +302,9 @@ def shard_partials(x: np.ndarray, chosen: np.ndarray, vocab_start: int, softcap:
     loc = np.asarray(chosen) - vocab_start
     inside = (loc >= 0) & (loc < x.shape[1])
     yc = np.where(inside, y[np.arange(x.shape[0]), np.clip(loc, 0, x.shape[1] - 1)], 0.0)
+    if temperature is not None and temperature != 1.0:
+        e2 = np.exp((y - M[:, None]) / temperature)
+        return np.stack([M, e.sum(axis=1), np.zeros_like(M), yc, e2.sum(axis=1), (e2 * y).sum(axis=1)], axis=1)
     return np.stack([M, e.sum(axis=1), (e * y).sum(axis=1), yc], axis=1)
 
 

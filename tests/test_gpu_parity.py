@@ -232,6 +232,51 @@ def test_vocab_shards_on_one_gpu(cuda, k, softcap):
         assert torch.equal(p.loss, probs[0].loss)
 
 
+def test_vocab_shards_entropy_at_other_temperatures(cuda):
+    """Entropy of softmax(y / temperature) from vocabulary shards: the partial record grows to six floats (two
+    more sums on y/temperature), merged like the others (MLLM_JAX/train_modules/__init__.py:136-138 under the
+    tp sharding of MLLM_JAX/utils.py:245)."""
+    from mllm_jax_b200 import _lib
+
+    B, L, V, k, temp = 2, 9, 4 * 1000, 4, 0.7
+    logits, inputs = make_case(B, L, V, seed=45, old="wide", ref=True)
+    logits[0, 2, 100:900] = float("-inf")
+    attrs = dict(beta=0.04, temperature=temp)
+    ref = O.reference_value_and_grad(logits, inputs, **attrs)
+    din = to_device(inputs, cuda)
+    x = logits.to(cuda)
+    cfg = G.LossConfig(beta=0.04, temperature=temp)
+    N, Vs = B * (L - 1), V // k
+    probs = []
+    for r in range(k):
+        p = G.TokenLossProblem(x[:, :, r * Vs:(r + 1) * Vs], din["input_ids"][:, 1:], din["labels"][:, 1:],
+                               din["advantages"], din["total_valid_token_count"], din["old_per_token_logps"],
+                               din["ref_per_token_logps"], cfg, scored_rows=L - 1, vocab=Vs, vocab_start=r * Vs,
+                               vocab_total=V)
+        probs.append(p)
+    width = int(_lib.load().mllm_grpo_partial_width(probs[0].args()))
+    assert width == 6
+    gathered = torch.empty(k, N, width, device=cuda)
+    for r, p in enumerate(probs):
+        p.partials = gathered[r]
+        p.run("mllm_grpo_fwd_partials")
+    want = np.stack([O.shard_partials(logits[:, :-1, r * Vs:(r + 1) * Vs].double().numpy().reshape(N, Vs),
+                                      inputs["input_ids"][:, 1:].numpy().reshape(-1), r * Vs, None, temp)
+                     for r in range(k)])
+    finite = np.isfinite(want)
+    assert np.allclose(gathered.cpu().numpy()[finite], want[finite], rtol=3e-4, atol=1e-5)
+    dfull = torch.empty_like(x)
+    for r, p in enumerate(probs):
+        p.gathered, p.n_shards = gathered, k
+        p.run("mllm_grpo_combine")
+        p.dlogits = dfull[:, :, r * Vs:(r + 1) * Vs]
+        p.run("mllm_grpo_bwd")
+    torch.cuda.synchronize()
+    got = {"loss": probs[0].loss[0], "per_token_logps": probs[0].per_token_logps,
+           "token_entropy": probs[0].token_entropy, "dlogits": dfull}
+    check(ref, got, "entropy from shards at temperature 0.7")
+
+
 @pytest.mark.parametrize("eager", [False, True])
 def test_golden_fixtures(cuda, eager):
     """Committed fixtures through both autograd forms: separate forward / backward kernels, and the
