@@ -40,7 +40,7 @@ METRIC = "fused GRPO loss fwd+bwd tokens/s"
 UNIT = "tokens/s"
 # DRAM bytes per logit element the one-kernel step moves (dram__bytes_read + dram__bytes_write of ncu
 # captures on small cases of the same kernels, see profiles/): one bf16 read + one bf16 write.
-NCU_TRAFFIC_PER_ELEMENT = {"two_pass_kernel": 4.003, "two_pass_kernel_softcap": 4.08, "two_pass_kernel_long_rows": 4.50}
+NCU_TRAFFIC_PER_ELEMENT = {"two_pass_kernel": 4.003, "two_pass_kernel_softcap": 4.08, "two_pass_kernel_long_rows": 4.10}
 CHUNK_BYTES = 45e9  # largest logits buffer per GPU; bigger batches run as row chunks over one buffer
 DEFAULT_EXTRA = "cfg2,cfg3,cfg4-65536"
 
@@ -459,9 +459,9 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
     roofline = {
         "bound": "hbm", "kernel": kernel, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
         "peak_kind": job.peak_kind, "ms_per_launch": ms_launch, "algorithmic_bytes_per_launch": bytes_launch,
-        # rows of 176 KB and more run as 4 CTAs x 128 threads and miss L2 on a quarter of their second reads
+        # rows of 192 KB and more run as 6 CTAs x 128 threads and miss L2 on 5 % of their second reads
         "traffic": NCU_TRAFFIC_PER_ELEMENT["two_pass_kernel_softcap" if w.softcap else (
-            "two_pass_kernel_long_rows" if (mode != "vocab" and 2 * v_local >= 176 * 1024) else "two_pass_kernel")] * v_local *
+            "two_pass_kernel_long_rows" if (mode != "vocab" and 2 * v_local >= 192 * 1024) else "two_pass_kernel")] * v_local *
         rows_chunk if one_kernel else None,
         "traffic_note": "dram__bytes_read + dram__bytes_write per logit element from ncu captures of small cases of "
                         "the same kernel (profiles/), scaled by the elements of one launch: traffic grows in proportion",
