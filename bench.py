@@ -347,6 +347,7 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
     rows_chunk = chunk_seqs * w.seq_len  # rows of one launch on this rank
 
     exchange = None
+    pending = []  # token-parallel: the loss all-reduce still in flight
     if mode == "single":
         data = synth.make_inputs(wc, seed=args.seed, device=str(dev))
         dlogits = torch.empty_like(data["logits"])
@@ -371,8 +372,13 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
         plan1 = first["problem"]
 
         def launch():
+            # the one exchange: a scalar all-reduce, issued every step without stalling the compute stream (the
+            # next step's kernel does not depend on it); the last one is waited for inside the timed region
             plan1.run("mllm_grpo_fwd_bwd", reuse_args=True)
-            first["loss"] = tp.reduce_loss(first["local_loss"])  # the one exchange: a scalar all-reduce
+            if pending:
+                pending.pop().wait()
+            first["loss"], work = tp.reduce_loss_async(first["local_loss"])
+            pending.append(work)
             return first
         parallelism = default_parallelism(world, mode, seqs_local)
         kernel = "two_pass_kernel (mllm_grpo_fwd_bwd on this rank's rows)"
@@ -415,8 +421,13 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
             out = launch()
         return out
 
+    def finish():  # token-parallel: the compute stream joins the last outstanding loss all-reduce
+        if mode == "token" and pending:
+            pending.pop().wait()
+
     for _ in range(max(warmup, 3)):
         out = step()
+    finish()
     job.barrier()
     sampler = ClockSampler(job.local)
     if rank == 0 and main:
@@ -428,6 +439,7 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
     ev0.record()
     for _ in range(steps):
         out = step()
+    finish()
     ev1.record()
     job.barrier()
     launches = _lib.launch_count() - launches0
@@ -446,6 +458,7 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
             dist.barrier()  # ranks enter the exchanging kernel together, as in the timed loop's steady state
         evs[0].record()
         launch()
+        finish()
         evs[1].record()
         torch.cuda.synchronize()
         if i >= 3:
@@ -505,7 +518,7 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
 
     e2e = None
     if main and not args.no_e2e and n_chunks == 1:
-        e2e = measure_e2e(data, launch, args, job)
+        e2e = measure_e2e(data, launch, args, job, finish)
     result = {
         "workload": w.name, "rows": N, "vocab": V, "ms_per_step": ms_per_step, "value": value,
         "valid_tokens_per_s": value * float(data["mask"].mean().item()), "loss": loss, "device_status": status,
@@ -516,7 +529,7 @@ def run_workload(job: Job, name: str, steps: int, warmup: int, main: bool) -> di
     return result
 
 
-def measure_e2e(data, step_fn, args, job: Job):
+def measure_e2e(data, step_fn, args, job: Job, finish=lambda: None):
     """Same metric through the public API with HOST buffers: per step, copy the step's inputs (this
     rank's shard when N > 1) from pinned host memory, run fwd+bwd through `step_fn`, read the loss and
     the per-token log-probs back.  Time = max over ranks."""
@@ -544,6 +557,7 @@ def measure_e2e(data, step_fn, args, job: Job):
         for k in names:
             data[k].copy_(host[k], non_blocking=True)
         out = step_fn()
+        finish()
         lp_host.copy_(out["per_token_logps"], non_blocking=True)
         loss_host.copy_(out["loss"], non_blocking=True)
         torch.cuda.synchronize()

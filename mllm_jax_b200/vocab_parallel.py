@@ -215,3 +215,11 @@ class TokenParallelLoss:
         total = local_loss.detach().clone()
         dist.all_reduce(total, op=dist.ReduceOp.SUM, group=self.group)
         return total
+
+    def reduce_loss_async(self, local_loss: torch.Tensor):
+        """The same sum without making the compute stream wait for it: returns (total, work).  Nothing after the
+        loss kernel depends on the global loss (the gradient is complete per rank), so the next step's kernel can
+        run while the scalar crosses NVLink; call work.wait() before reading `total`."""
+        total = local_loss.detach().clone()
+        work = dist.all_reduce(total, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        return total, work
