@@ -101,7 +101,15 @@ void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, i
   *cluster = cl;
   *threads = th;
   *smem = sm;
-  *unroll = (un == 6 || un == 10) ? un : 8;
+  if (cl == 1 && f_un <= 0) {
+    // Unsplit rows through registers with 256 threads: a thread owns n vectors per pass.  Longer rows want more of
+    // them in flight per batch (64 instead of 48 registers, 4 instead of 5 CTAs per SM).  Measured on one B200,
+    // batches of 4 / 6 / 8: n = 18.5 (76 KB) 0.821 / 0.834 / 0.826 ms unsharded, 0.863 / 0.828 / 0.887 sharded;
+    // n = 24.4 (100 KB) 1.128 / 1.085 / 1.061 unsharded; n = 37.1 (148 KB) 1.904 / 1.875 / 1.774 sharded.
+    const double n = double(nvec) / 256.0;
+    un = n >= 22.0 ? 8 : (sharded && n >= 12.0 ? 6 : 4);
+  }
+  *unroll = (un == 4 || un == 6 || un == 10) ? un : 8;
 }
 
 // *taken is false (nothing launched) when logits and dlogits rows do not share their 16-byte phase.

@@ -287,6 +287,10 @@ cudaError_t launch_t(const KernelParams& p, int ent, int threads, int unroll, bo
     if (threads <= 128 && unroll == 10) return launch_e<CL, 128, 10, SHARDED>(p, ent, smem, s);
   }
   if (threads <= 128) return launch_e<CL, 128, 8, SHARDED>(p, ent, smem, s);
+  if constexpr (CL == 1) {  // unsplit rows through registers, 256 threads: batches of 4, 6 or 8 (the plan's choice)
+    if (threads <= 256 && !smem && unroll == 6) return launch_e<1, 256, 6, SHARDED>(p, ent, smem, s);
+    if (threads <= 256 && !smem && unroll == 8) return launch_e<1, 256, 8, SHARDED>(p, ent, smem, s);
+  }
   if (threads <= 256 || CL > 1) return launch_e<CL, 256, 4, SHARDED>(p, ent, smem, s);
   return launch_e<CL, 512, 4, SHARDED>(p, ent, smem, s);
 }
