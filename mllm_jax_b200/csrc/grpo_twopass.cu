@@ -106,8 +106,10 @@ void two_pass_plan(const KernelParams& p, int ent, bool sharded, int* cluster, i
     // them in flight per batch (64 instead of 48 registers, 4 instead of 5 CTAs per SM).  Measured on one B200,
     // batches of 4 / 6 / 8: n = 18.5 (76 KB) 0.821 / 0.834 / 0.826 ms unsharded, 0.863 / 0.828 / 0.887 sharded;
     // n = 24.4 (100 KB) 1.128 / 1.085 / 1.061 unsharded; n = 37.1 (148 KB) 1.904 / 1.875 / 1.774 sharded.
+    // The soft-cap kernels (more registers per vector) stay at 4: 65536 rows, 128 KB shards 3.71 / 3.73 / 4.21 ms,
+    // 64 KB shards 1.98 / 2.16 / 2.56, 100 KB unsharded 2.78 / 2.85 / 3.09.
     const double n = double(nvec) / 256.0;
-    un = n >= 22.0 ? 8 : (sharded && n >= 12.0 ? 6 : 4);
+    un = p.softcap > 0.f ? 4 : (n >= 22.0 ? 8 : (sharded && n >= 12.0 ? 6 : 4));
   }
   *unroll = (un == 4 || un == 6 || un == 10) ? un : 8;
 }

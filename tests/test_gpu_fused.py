@@ -135,7 +135,7 @@ def test_fused_equals_two_sweeps_closely(cuda):
 @pytest.mark.parametrize("sweeps,cluster,threads,batch,staged", [
     (0, 1, 512, 0, -1), (0, 1, 128, 0, 0), (0, 1, 64, 0, 0), (0, 1, 256, 0, 1), (0, 2, 256, 0, -1),
     (0, 4, 256, 0, -1), (0, 4, 128, 6, -1), (0, 8, 128, 10, -1), (0, 2, 128, 8, -1), (0, 6, 128, 6, -1),
-    (0, 6, 128, 8, -1), (0, 0, 0, 0, -1),
+    (0, 6, 128, 8, -1), (0, 1, 256, 6, 0), (0, 1, 256, 8, 0), (0, 0, 0, 0, -1),
     (1, 0, 0, 0, -1)])
 @pytest.mark.parametrize("kind", ["kl", "softcap", "shifted_tail"])
 def test_every_fwd_bwd_plan(cuda, sweeps, cluster, threads, batch, staged, kind):
