@@ -67,10 +67,65 @@ __device__ __forceinline__ float4 merge_partials(const float4* parts, int count)
   return make_float4(M, S, U, yc);
 }
 
+// Waits, bounded, until the four words at `src` (a slot of THIS rank's exchange buffer) carry the call's
+// epoch and returns their value halves.  *lost is set when the wait was given up: its own limit ran out
+// (the status bit is raised), or some wait of this call, or an uncleared earlier one, already had.
+struct WaitedPartial {
+  float4 v;
+  int lost;
+};
+// Not inlined: the wait runs once per row in a few threads, and its loop state must not raise the register
+// count of the streaming passes around it.
+static __device__ __noinline__ WaitedPartial wait_partial_words(const unsigned long long* src, uint32_t want,
+                                                        unsigned long long wait_ns, int32_t* status_word) {
+  int lost = 0;
+  unsigned long long w0, w1, w2, w3;
+  unsigned long long t0 = 0;
+  const volatile int32_t* status = status_word;
+  for (int spin = 0;; ++spin) {
+    ld_words2_sys(src, w0, w1);  // all four words in one round trip
+    ld_words2_sys(src + 2, w2, w3);
+    if (static_cast<uint32_t>(w0 >> 32) == want && static_cast<uint32_t>(w1 >> 32) == want &&
+        static_cast<uint32_t>(w2 >> 32) == want && static_cast<uint32_t>(w3 >> 32) == want)
+      break;
+    if ((spin & 63) == 0 && (*status & MLLM_GRPO_DEV_WAIT_TIMEOUT)) {
+      lost = 1;
+      break;
+    }
+    if (t0 == 0) t0 = cl::globaltimer();
+    if (cl::globaltimer() - t0 > wait_ns) {
+      atomicOr(status_word, MLLM_GRPO_DEV_WAIT_TIMEOUT);
+      lost = 1;
+      break;
+    }
+    __nanosleep(32);
+  }
+  WaitedPartial r;
+  r.v = make_float4(__uint_as_float(static_cast<uint32_t>(w0)), __uint_as_float(static_cast<uint32_t>(w1)),
+                    __uint_as_float(static_cast<uint32_t>(w2)), __uint_as_float(static_cast<uint32_t>(w3)));
+  r.lost = lost;
+  return r;
+}
+__device__ __forceinline__ float4 wait_partial(const KernelParams& p, const unsigned long long* src, bool* lost) {
+  const WaitedPartial r = wait_partial_words(src, static_cast<uint32_t>(p.exchange_epoch), p.peer_wait_ns, p.device_status);
+  if (r.lost) *lost = true;
+  return r.v;
+}
+
+__device__ __forceinline__ void push_partial(const KernelParams& p, unsigned long long* dst, const float4& v) {
+  st_words2_sys(dst, make_word(v.x, p.exchange_epoch), make_word(v.y, p.exchange_epoch));
+  st_words2_sys(dst + 2, make_word(v.z, p.exchange_epoch), make_word(v.w, p.exchange_epoch));
+}
+
 // SMEM: the CTA's row slice is brought into shared memory by one bulk (TMA) copy and both passes read
 // it from there: no load registers, the whole slice in flight at once, and no second trip to L2.
+// The unsplit sharded 256-thread kernels with short load batches are held to 5 CTAs per SM (51 registers): the
+// warp-level exchange must not cost them a resident CTA.  0 = no minimum asked for.
+template <int CL, int THREADS, int UNROLL, bool CAP, bool SHARDED, bool SMEM>
+constexpr int kMinCtasPerSm = (SHARDED && CL == 1 && THREADS == 256 && !SMEM && !CAP && UNROLL <= 6) ? 5 : 0;
+
 template <int CL, int THREADS, int UNROLL, int ENT, bool CAP, bool SHARDED, bool SMEM>
-__global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p, const int64_t vec_per) {
+__global__ void __launch_bounds__(THREADS, kMinCtasPerSm<CL, THREADS, UNROLL, CAP, SHARDED, SMEM>) two_pass_kernel(const KernelParams p, const int64_t vec_per) {
   extern __shared__ __align__(128) unsigned char slice_smem[];
   __shared__ unsigned long long load_bar;
   __shared__ int abort_flag;
@@ -100,7 +155,7 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
   }
   // Tell the cluster peers this CTA is running (its shared memory exists) without blocking yet.
   if (CL > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
-  if (SHARDED && tid == 0) peer_lost = 0;  // ordered before its writers by the barrier inside the first pass
+  if (SHARDED && CL > 1 && tid == 0) peer_lost = 0;  // ordered before its writers by the barrier inside the first pass
   if (SMEM && tid == 0) {
     abort_flag = 0;
     const uint32_t bar = cl::smem_u32(&load_bar);
@@ -135,64 +190,56 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
   const RowStats st = row_pass1<THREADS, UNROLL, ENT, CAP, SMEM ? 3 : 2>(xs, ncol, p.inv_temperature, sc, red, keep);
   if (CAP && tid < 8 && cl_local >= 0 && cl_local < ncol) yc_own = sc.y(yc_own);
 
+  // Unsplit sharded rows: warp 0 alone pushes, waits, merges and finishes the token (every thread holds the
+  // row's statistics and lanes < 8 the chosen logit), so no block barrier stands between the first pass's
+  // reduction and the one that publishes (g, lse) to the second pass.
+  constexpr bool WARP_EXCHANGE = SHARDED && CL == 1;
   if (CL > 1) {
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
     if (tid < CL)
       cl::st_cluster_f4(cl::map_to_cta(cl::smem_u32(&slots[rank]), tid), make_float4(st.M, st.S, st.U, yc_own));
     cl::cluster_sync_all();  // release our pushes, acquire everyone else's
-  } else if (tid == 0) {
+  } else if (!WARP_EXCHANGE && tid == 0) {
     slots[0] = make_float4(st.M, st.S, st.U, yc_own);
   }
 
   TokenSide side = {};
-  if (SHARDED) {
+  float4 merged = make_float4(0.f, 0.f, 0.f, 0.f);
+  bool lost = false;
+  if (WARP_EXCHANGE) {
+    if (tid < 32) {
+      const int k = p.n_shards, me = p.shard_rank;
+      const int64_t N = p.n_seqs * p.scored_rows;
+      const int64_t half = int64_t(p.exchange_epoch & 1) * int64_t(k) * N;  // parity half of every buffer
+      float4 part = make_float4(kNegInit, 0.f, 0.f, 0.f);
+      if (tid < k) push_partial(p, p.peer_words[tid] + (half + int64_t(me) * N + n) * 4, make_float4(st.M, st.S, st.U, yc_own));
+      // The epilogue's side inputs are requested now, so that their latency runs beside the exchange's.
+      if (tid == 0) side = load_token_side(p, n, b);
+      if (tid < k) part = wait_partial(p, p.peer_words[me] + (half + int64_t(tid) * N + n) * 4, &lost);
+      lost = __any_sync(0xffffffffu, lost);
+      const float M = warp_max(part.x);
+      const float e = tid < k ? ex2f((part.x - M) * kLog2e) : 0.f;
+      merged = make_float4(M, warp_sum(part.y * e), warp_sum(part.z * e), warp_sum(tid < k ? part.w : 0.f));
+    }
+  } else if (SHARDED) {
     const int k = p.n_shards, me = p.shard_rank;
     const int64_t N = p.n_seqs * p.scored_rows;
-    const int64_t half = int64_t(p.exchange_epoch & 1) * int64_t(k) * N;  // parity half of every buffer
-    if (CL == 1) __syncthreads();                                          // slots[0] visible to threads < k
-    // The epilogue's side inputs are requested now, so that their latency runs beside the exchange's.
+    const int64_t half = int64_t(p.exchange_epoch & 1) * int64_t(k) * N;
     if (tid == 0) side = load_token_side(p, n, b);
     if (tid < k) {
-      if (rank == 0) {  // one CTA per row talks to the other GPUs
-        const float4 mine = merge_partials(slots, CL);
-        unsigned long long* dst = p.peer_words[tid] + (half + int64_t(me) * N + n) * 4;
-        st_words2_sys(dst, make_word(mine.x, p.exchange_epoch), make_word(mine.y, p.exchange_epoch));
-        st_words2_sys(dst + 2, make_word(mine.z, p.exchange_epoch), make_word(mine.w, p.exchange_epoch));
-      }
-      // wait for rank `tid`'s partial of this row in OUR buffer: all four words in one round trip
-      const unsigned long long* src = p.peer_words[me] + (half + int64_t(tid) * N + n) * 4;
-      const uint32_t want = static_cast<uint32_t>(p.exchange_epoch);
-      unsigned long long w0, w1, w2, w3;
-      unsigned long long t0 = 0;
-      const volatile int32_t* status = p.device_status;
-      for (int spin = 0;; ++spin) {
-        ld_words2_sys(src, w0, w1);
-        ld_words2_sys(src + 2, w2, w3);
-        if (static_cast<uint32_t>(w0 >> 32) == want && static_cast<uint32_t>(w1 >> 32) == want &&
-            static_cast<uint32_t>(w2 >> 32) == want && static_cast<uint32_t>(w3 >> 32) == want)
-          break;
-        // Some wait of this call (or an uncleared earlier one) already ran out: do not wait again.
-        if ((spin & 63) == 0 && (*status & MLLM_GRPO_DEV_WAIT_TIMEOUT)) {
-          peer_lost = 1;
-          break;
-        }
-        if (t0 == 0) t0 = cl::globaltimer();
-        if (cl::globaltimer() - t0 > p.peer_wait_ns) {
-          atomicOr(p.device_status, MLLM_GRPO_DEV_WAIT_TIMEOUT);
-          peer_lost = 1;
-          break;
-        }
-        __nanosleep(32);
-      }
-      const float got[4] = {__uint_as_float(static_cast<uint32_t>(w0)), __uint_as_float(static_cast<uint32_t>(w1)),
-                            __uint_as_float(static_cast<uint32_t>(w2)), __uint_as_float(static_cast<uint32_t>(w3))};
-      parts[tid] = make_float4(got[0], got[1], got[2], got[3]);
+      // one CTA per row talks to the other GPUs
+      if (rank == 0) push_partial(p, p.peer_words[tid] + (half + int64_t(me) * N + n) * 4, merge_partials(slots, CL));
+      // wait for rank `tid`'s partial of this row in OUR buffer
+      bool gave_up = false;
+      parts[tid] = wait_partial(p, p.peer_words[me] + (half + int64_t(tid) * N + n) * 4, &gave_up);
+      if (gave_up) peer_lost = 1;
     }
+    __syncthreads();  // parts[] were written by threads 0..k-1
+    lost = peer_lost != 0;
   }
   // Unsharded: thread 0 reads slots it wrote itself (CL == 1) or acquired at the cluster barrier (CL > 1).
-  if (SHARDED) __syncthreads();  // parts[] were written by threads 0..k-1
   if (tid == 0) {
-    const float4 m = SHARDED ? merge_partials(parts, p.n_shards) : merge_partials(slots, CL);
+    const float4 m = WARP_EXCHANGE ? merged : (SHARDED ? merge_partials(parts, p.n_shards) : merge_partials(slots, CL));
     RowStats all;
     all.M = m.x;
     all.S = m.y;
@@ -200,7 +247,7 @@ __global__ void __launch_bounds__(THREADS) two_pass_kernel(const KernelParams p,
     all.S2 = st.S2;  // temperature != 1 entropy exists only unsplit (CL == 1, not sharded)
     all.U2 = st.U2;
     TokenOut o = SHARDED ? token_epilogue_core<ENT>(p, all, m.w, side) : token_epilogue<ENT>(p, n, b, all, m.w);
-    if (SHARDED && peer_lost) {  // merged stale words: make the row unusable instead of silently wrong
+    if (SHARDED && lost) {  // merged stale words: make the row unusable instead of silently wrong
       o.lp = o.entropy = o.loss_term = __int_as_float(0x7fc00000);
       o.grad_coef = 0.f;
     }
