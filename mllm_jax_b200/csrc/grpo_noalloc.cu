@@ -6,7 +6,7 @@
 // call site did not declare an extra result to serve as workspace there is nothing to pass as
 // `loss_terms`, and calling cudaMalloc from the handler is off the table (it synchronises the
 // device and takes memory behind the back of the framework's own pool).  The same holds for a
-// serving loop that promised its latency budget "no allocator calls after start-up".
+// serving loop that promised "no allocator calls after start-up" to keep its latency bounded.
 //
 // What it does instead: the per-token loss terms go to a fixed array that lives in the library's
 // own device image.  The array costs MLLM_GRPO_STATIC_SCRATCH_TOKENS * 4 bytes (4 MiB) on every

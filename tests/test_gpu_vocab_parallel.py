@@ -63,7 +63,22 @@ def _run_rank(rank, world, port, ret):
             assert (out["token_entropy"].cpu() - ref["token_entropy"]).abs().max() <= ENT_ATOL, name
             assert_loss_close(out["loss"].item(), ref["loss"].item(), what=name)
             assert_dlogits_close(out["dlogits"], want_d, what=name)
-        # soft-capped logits through the fused path (staged shards compute their exponentials during the exchange)
+        # every sharded kernel family behind the fused entry: register-fed unsplit rows in load batches of 4, 6 and 8
+        # (warp-level exchange), shards split over clusters of 2, 4 and 8 CTAs, and the staged form again
+        from mllm_jax_b200._lib import plan_override
+
+        for cluster, threads, batch, staged in [(1, 256, 4, 0), (1, 256, 6, 0), (1, 256, 8, 0), (1, 128, 8, 0),
+                                                (2, 128, 10, -1), (4, 128, 8, -1), (8, 128, 6, -1), (1, 256, 0, 1)]:
+            name = f"plan cl={cluster} th={threads} batch={batch} staged={staged}"
+            with plan_override(cluster=cluster, threads=threads, load_batch=batch, staged=staged):
+                out = vp.value_and_grad_fused(*args, dlogits=torch.empty_like(shard))
+                torch.cuda.synchronize()
+            assert G.ops.check_device_status(out["problem"]) == 0, name
+            assert (out["per_token_logps"].cpu() - ref["per_token_logps"]).abs().max() <= LP_ATOL, name
+            assert (out["token_entropy"].cpu() - ref["token_entropy"]).abs().max() <= ENT_ATOL, name
+            assert_loss_close(out["loss"].item(), ref["loss"].item(), what=name)
+            assert_dlogits_close(out["dlogits"], want_d, what=name)
+        # soft-capped logits through the fused path
         big, big_in = make_case(B, L, V, seed=96, old="wide", ref=True, sigma=6.0)
         cap_attrs = dict(beta=0.04, epsilon_low=0.2, epsilon_high=0.3, softcap=30.0)
         ref_c = O.reference_value_and_grad(big, big_in, **cap_attrs)
