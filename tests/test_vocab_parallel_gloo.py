@@ -45,6 +45,11 @@ def _worker(rank, world, port, ret):
         from mllm_jax_b200.vocab_parallel import TokenParallelLoss
         total = TokenParallelLoss().reduce_loss(torch.tensor(float(rank + 1)))
         assert total.item() == sum(range(1, world + 1))
+        # the form that does not make the caller wait: the local value is left alone, the sum is ready after wait()
+        local = torch.tensor(float(10 * (rank + 1)))
+        total2, work = TokenParallelLoss().reduce_loss_async(local)
+        work.wait()
+        assert total2.item() == 10 * sum(range(1, world + 1)) and local.item() == 10 * (rank + 1)
         # a mismatched buffer is refused before any communication
         try:
             exchange_partials(mine, out=torch.empty(world, N + 1, 4))
