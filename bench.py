@@ -534,18 +534,22 @@ def measure_e2e(data, step_fn, args, job: Job, finish=lambda: None):
     rank's shard when N > 1) from pinned host memory, run fwd+bwd through `step_fn`, read the loss and
     the per-token log-probs back.  Time = max over ranks."""
     dist, dev = job.dist, job.dev
+    from mllm_jax_b200 import host_io
+
     names = ("logits", "token_ids", "mask", "advantages", "old_logps", "ref_logps")
     host = {}
-    try:
-        for k in names:
-            host[k] = torch.empty(data[k].shape, dtype=data[k].dtype, pin_memory=True)
-            host[k].copy_(data[k])
-    except RuntimeError as e:  # not enough pinnable host memory
-        return {"value": None, "unit": UNIT, "error": str(e)[:120]}
-    torch.cuda.synchronize()
-    n_local = data["token_ids"].numel()
-    lp_host = torch.empty(data["token_ids"].shape, dtype=torch.float32, pin_memory=True)
-    loss_host = torch.empty((), dtype=torch.float32, pin_memory=True)
+    # the staging buffers are allocated on the GPU's own NUMA node where sysfs names it (None: left where they fall)
+    with host_io.near_gpu(dev.index if dev.index is not None else torch.cuda.current_device()) as numa_node:
+        try:
+            for k in names:
+                host[k] = torch.empty(data[k].shape, dtype=data[k].dtype, pin_memory=True)
+                host[k].copy_(data[k])
+        except RuntimeError as e:  # not enough pinnable host memory
+            return {"value": None, "unit": UNIT, "error": str(e)[:120]}
+        torch.cuda.synchronize()
+        n_local = data["token_ids"].numel()
+        lp_host = torch.empty(data["token_ids"].shape, dtype=torch.float32, pin_memory=True)
+        loss_host = torch.empty((), dtype=torch.float32, pin_memory=True)
     steps = max(2, min(args.steps, 5))
     h2d = sum(host[k].numel() * host[k].element_size() for k in names)
     d2h = lp_host.numel() * 4 + 4
@@ -569,6 +573,7 @@ def measure_e2e(data, step_fn, args, job: Job, finish=lambda: None):
     sec = ms * 1e-3 / steps
     return {"value": n_local * (world if token_mode else 1) / sec, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
             "d2h_bytes_per_step": d2h * world, "ms_per_step": sec * 1e3, "steps": steps,
+            "pinned_numa_node": numa_node,
             "note": "every rank copies its logits shard over its own PCIe link each step; dlogits stay on the "
                     "device for the lm_head backward"}
 

@@ -124,3 +124,23 @@ def test_workload_names_and_chunking():
     # cfg1 never chunks
     c1 = synth.CONFIGS["cfg1"]
     assert bench.chunking(c1, c1.n_seqs, c1.vocab) == (c1.n_seqs, 1)
+
+
+def test_pinned_buffer_placement_reads_sysfs(tmp_path):
+    """The NUMA helpers parse sysfs as laid out by Linux and do nothing where it is silent."""
+    from mllm_jax_b200 import host_io
+
+    assert host_io.parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert host_io.parse_cpulist("") == set()
+    dev = tmp_path / "bus/pci/devices/0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices/system/node/node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("4-7\n")
+    assert host_io.numa_node_of("0000:1b:00.0", str(tmp_path)) == 1
+    assert host_io.cpus_of_node(1, str(tmp_path)) == {4, 5, 6, 7}
+    (dev / "numa_node").write_text("-1\n")
+    assert host_io.numa_node_of("0000:1b:00.0", str(tmp_path)) is None
+    assert host_io.numa_node_of("0000:ff:00.0", str(tmp_path)) is None
+    assert host_io.cpus_of_node(3, str(tmp_path)) == set()
